@@ -100,8 +100,9 @@ class CacheManager:
     """Owns the pages, the block tables and the state slots of all live requests.
 
     ``layout`` maps a layer index to its ``CacheSpec`` (layers without a cache of their
-    own are absent).  ``n_pages`` is the size of each full-attention group's pool;
-    a window group gets what ``max_slots`` requests can hold at once.
+    own are absent), or to a tuple of them when a layer keeps pages and a state of fixed
+    size (at most one of each kind).  ``n_pages`` is the size of each full-attention group's
+    pool; a window group gets what ``max_slots`` requests can hold at once.
     """
 
     def __init__(self, layout: Dict[int, object], n_pages: int, max_slots: int, dtype: torch.dtype, device,
@@ -118,8 +119,13 @@ class CacheManager:
         self.group_of_layer: Dict[int, int] = {}
         self.state_group_of_layer: Dict[int, int] = {}
         by_spec: Dict[object, int] = {}
+        entries = []
         for layer in sorted(layout):
-            spec = layout[layer]
+            specs = layout[layer] if isinstance(layout[layer], (tuple, list)) else (layout[layer],)
+            if sum(isinstance(sp, PagedKV) for sp in specs) > 1 or sum(isinstance(sp, FixedState) for sp in specs) > 1:
+                raise TypeError(f"layer {layer}: at most one paged cache and one fixed state per layer, not {specs!r}")
+            entries += [(layer, sp) for sp in specs]
+        for layer, spec in entries:
             if isinstance(spec, PagedKV):
                 if spec not in by_spec:
                     pages = n_pages

@@ -48,6 +48,7 @@ LIBRARIES: Dict[str, tuple] = {
     "delta_rule": ("delta_rule.cu", []),
     "attention_heads": ("attention_heads.cu", []),
     "moe": ("moe.cu", []),
+    "token_mix": ("token_mix.cu", []),
 }
 
 _HEADERS = ["common.cuh", "page_map.cuh"]

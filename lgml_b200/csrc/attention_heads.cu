@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
     const float *__restrict__ freq, const float *__restrict__ freq_lo, int n_rot, const int *__restrict__ positions,
     const int *__restrict__ seq_of_token, const int *__restrict__ block_table, int max_blocks, T *__restrict__ k_pages, int n_pages,
     int page_size, T *__restrict__ q_plain, int ldqplain, T *__restrict__ q_full, int ldqfull, int H, int D, int Dr, int R, int write_kv,
-    int *__restrict__ status) {
+    float rot_mag, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float cs[];       // cos, then sin, of the n_rot / 2 angles
@@ -73,7 +73,12 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
     const int pos = positions[t];
     const int half = n_rot / 2;
     float *sn = cs + half;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) rope_sincos(pos, freq[i], freq_lo ? freq_lo[i] : 0.f, &sn[i], &cs[i]);
+    // rot_mag: a factor on every cosine and sine (frequency scalings that lengthen the rotated vectors); 1 changes no bit
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sv, cv;
+        rope_sincos(pos, freq[i], freq_lo ? freq_lo[i] : 0.f, &sv, &cv);
+        sn[i] = sv * rot_mag, cs[i] = cv * rot_mag;
+    }
     const float *drow = dkv + (size_t)t * lddkv;
     float ss = 0.f;
     if (write_kv)
@@ -121,12 +126,15 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
     }
 }
 
+// an output gate: the product times sigmoid(gate[t, h oh + o]) (float32 logits of a projection of the mixer's input)
+__device__ __forceinline__ float gate_sigmoid(float g) { return 1.0f / (1.0f + expf(-g)); }
+
 // out[t, h oh + o] = sum_k x[t, h xh + k] w[h][o][k]; float32 sums, k in order, so a row's result
 // does not depend on what else is in the batch.  A block: 32 tokens x 64 outputs of one head.
 constexpr int HL_TM = 32, HL_TN = 64, HL_TK = 32;
 template <typename T>
 __global__ void __launch_bounds__(256) head_linear_kernel(const T *__restrict__ x, int ldx, int xh, const T *__restrict__ w, T *__restrict__ out,
-                                                          int ldo, int oh, int n, int O, int K) {
+                                                          int ldo, int oh, int n, int O, int K, const float *__restrict__ gate, int ldg) {
     pdl_trigger();
     pdl_wait();
     __shared__ float xs[HL_TM][HL_TK + 1];
@@ -168,7 +176,11 @@ __global__ void __launch_bounds__(256) head_linear_kernel(const T *__restrict__ 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int t = t0 + ty + 16 * i, o = o0 + tx + 16 * j;
-            if (t < n && o < O) out[(size_t)t * ldo + (size_t)h * oh + o] = from_f32<T>(acc[i][j]);
+            if (t < n && o < O) {
+                float v = acc[i][j];
+                if (gate) v *= gate_sigmoid(act_load(gate + (size_t)t * ldg + (size_t)h * oh + o));
+                out[(size_t)t * ldo + (size_t)h * oh + o] = from_f32<T>(v);
+            }
         }
 }
 
@@ -178,7 +190,8 @@ __global__ void __launch_bounds__(256) head_linear_kernel(const T *__restrict__ 
 constexpr int HM_T = 64, HM_K = 64, HM_LD = HM_K + 8;
 __device__ __forceinline__ uint32_t hm_smem(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __global__ void __launch_bounds__(128) head_linear_mma_kernel(const __nv_bfloat16 *__restrict__ x, int ldx, int xh, const __nv_bfloat16 *__restrict__ w,
-                                                              __nv_bfloat16 *__restrict__ out, int ldo, int oh, int n, int O, int K) {
+                                                              __nv_bfloat16 *__restrict__ out, int ldo, int oh, int n, int O, int K,
+                                                              const float *__restrict__ gate, int ldg) {
     pdl_trigger();
     pdl_wait();
     __shared__ __align__(16) __nv_bfloat16 As[HM_T * HM_LD];
@@ -233,7 +246,11 @@ __global__ void __launch_bounds__(128) head_linear_mma_kernel(const __nv_bfloat1
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 const int o = o0 + nt * 8 + (lane & 3) * 2 + i;
-                if (o < O) out[(size_t)t * ldo + (size_t)h * oh + o] = __float2bfloat16_rn(acc[nt][rr * 2 + i]);
+                if (o < O) {
+                    float v = acc[nt][rr * 2 + i];
+                    if (gate) v *= gate_sigmoid(act_load(gate + (size_t)t * ldg + (size_t)h * oh + o));
+                    out[(size_t)t * ldo + (size_t)h * oh + o] = __float2bfloat16_rn(v);
+                }
             }
     }
 }
@@ -258,7 +275,7 @@ LGML_API int lgml_diff_combine(const void *in, int in_dtype, int ldi, void *out,
 LGML_API int lgml_latent_prepare(const float *qp, int ldqp, const float *dkv, int lddkv, const float *norm_w, float eps, const float *freq,
                                  const float *freq_lo, int n_rot, const int *positions, const int *seq_of_token, const int *block_table,
                                  int max_blocks, void *k_pages, int dtype, int n_pages, int page_size, void *q_plain, int ldqplain, void *q_full,
-                                 int ldqfull, int n_tokens, int H, int D, int Dr, int R, int write_kv, int *status, cudaStream_t stream) {
+                                 int ldqfull, int n_tokens, int H, int D, int Dr, int R, int write_kv, float rot_mag, int *status, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && H > 0 && D > 0 && Dr >= 0 && R > 0 && page_size > 0 && max_blocks > 0, "latent_prepare: bad sizes");
     LGML_REQUIRE(n_rot >= 0 && n_rot <= Dr && n_rot % 2 == 0, "latent_prepare: %d rotated entries of %d", n_rot, Dr);
     LGML_REQUIRE(ldqp >= H * (D + Dr) && lddkv >= R + Dr && ldqplain >= H * D && ldqfull >= H * (R + Dr), "latent_prepare: row strides below the rows");
@@ -268,11 +285,11 @@ LGML_API int lgml_latent_prepare(const float *qp, int ldqp, const float *dkv, in
     if (dtype == LGML_F32)
         lgml_launch(latent_prepare_kernel<float>, n_tokens, 128, smem, stream, qp, ldqp, dkv, lddkv, norm_w, eps, freq, freq_lo, n_rot, positions,
                     seq_of_token, block_table, max_blocks, (float *)k_pages, n_pages, page_size, (float *)q_plain, ldqplain, (float *)q_full, ldqfull,
-                    H, D, Dr, R, write_kv, status);
+                    H, D, Dr, R, write_kv, rot_mag, status);
     else if (dtype == LGML_BF16)
         lgml_launch(latent_prepare_kernel<__nv_bfloat16>, n_tokens, 128, smem, stream, qp, ldqp, dkv, lddkv, norm_w, eps, freq, freq_lo, n_rot,
                     positions, seq_of_token, block_table, max_blocks, (__nv_bfloat16 *)k_pages, n_pages, page_size, (__nv_bfloat16 *)q_plain,
-                    ldqplain, (__nv_bfloat16 *)q_full, ldqfull, H, D, Dr, R, write_kv, status);
+                    ldqplain, (__nv_bfloat16 *)q_full, ldqfull, H, D, Dr, R, write_kv, rot_mag, status);
     else
         LGML_FAIL("latent_prepare: unknown type %d", dtype);
     return lgml_launch_status("latent_prepare");
@@ -280,22 +297,22 @@ LGML_API int lgml_latent_prepare(const float *qp, int ldqp, const float *dkv, in
 
 // x: [n, ldx] with head h at column h xh; w: [H, O, K] contiguous; out: [n, ldo] with head h at column h oh.
 LGML_API int lgml_head_linear(const void *x, int ldx, int xh, const void *w, void *out, int ldo, int oh, int dtype, int n_tokens, int H, int O,
-                              int K, cudaStream_t stream) {
+                              int K, const float *gate, int ldg, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && H > 0 && O > 0 && K > 0, "head_linear: bad sizes");
     LGML_REQUIRE(H <= 65535 && (O + HL_TN - 1) / HL_TN <= 65535, "head_linear: too many heads or outputs");
     if (n_tokens == 0) return 0;
     if (dtype == LGML_BF16 && n_tokens >= 32 && K % 8 == 0 && ldx % 8 == 0 && xh % 8 == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0) {
         dim3 gm((n_tokens + HM_T - 1) / HM_T, (O + HM_T - 1) / HM_T, H);
         lgml_launch(head_linear_mma_kernel, gm, 128, 0, stream, (const __nv_bfloat16 *)x, ldx, xh, (const __nv_bfloat16 *)w, (__nv_bfloat16 *)out, ldo, oh,
-                    n_tokens, O, K);
+                    n_tokens, O, K, gate, ldg);
         return lgml_launch_status("head_linear");
     }
     dim3 grid((n_tokens + HL_TM - 1) / HL_TM, (O + HL_TN - 1) / HL_TN, H);
     if (dtype == LGML_F32)
-        lgml_launch(head_linear_kernel<float>, grid, 256, 0, stream, (const float *)x, ldx, xh, (const float *)w, (float *)out, ldo, oh, n_tokens, O, K);
+        lgml_launch(head_linear_kernel<float>, grid, 256, 0, stream, (const float *)x, ldx, xh, (const float *)w, (float *)out, ldo, oh, n_tokens, O, K, gate, ldg);
     else if (dtype == LGML_BF16)
         lgml_launch(head_linear_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16 *)x, ldx, xh, (const __nv_bfloat16 *)w,
-                    (__nv_bfloat16 *)out, ldo, oh, n_tokens, O, K);
+                    (__nv_bfloat16 *)out, ldo, oh, n_tokens, O, K, gate, ldg);
     else
         LGML_FAIL("head_linear: unknown type %d", dtype);
     return lgml_launch_status("head_linear");

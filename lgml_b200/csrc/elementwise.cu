@@ -156,6 +156,7 @@ struct Args {
     float eps;
     int cs;
     int vec;      // rows, parts and vectors allow 16-byte accesses (8-byte for bfloat16)
+    float delta_scale = 1.0f;     // x += delta_scale * delta (a residual multiplier; 1: the plain sum, bit for bit)
 };
 
 // d += parts 1 .. n_parts - 1 of one quad, in order.  The loads of up to eight parts are issued
@@ -191,7 +192,7 @@ __device__ __forceinline__ void add_delta(const Args &a, float *xr, const TD *dr
         for (int q = 0; q < PER; ++q) d[q] += bq[q];
     }
 #pragma unroll
-    for (int q = 0; q < PER; ++q) v[q] += d[q];
+    for (int q = 0; q < PER; ++q) v[q] = fmaf(a.delta_scale, d[q], v[q]);
     if (!a.rows) store_quad(xr, i, c1, a.vec, v);
 }
 
@@ -251,7 +252,7 @@ __global__ void __launch_bounds__(MODE == 2 ? GROUP * MAX_CS : GROUP) rmsnorm_ke
                     for (int q = 0; q < PER; ++q) d[q] += bq[q];
                 }
 #pragma unroll
-                for (int q = 0; q < PER; ++q) v[k][rd][q] += d[q];
+                for (int q = 0; q < PER; ++q) v[k][rd][q] = fmaf(a.delta_scale, d[q], v[k][rd][q]);
                 if (!a.rows) store_quad(xr, i, c1, vec, v[k][rd]);
             }
     }
@@ -428,8 +429,9 @@ static int rmsnorm_launch(const rms::Args &a, int n_rows, cudaStream_t stream) {
 template <typename TD>
 static int rmsnorm_dispatch(float *x, const TD *delta, int n_parts, long long part_stride, const float *delta_bias,
                             const float *weight, const int *rows, void *out, int out_dtype, int n_rows, int width, float eps,
-                            cudaStream_t stream) {
+                            float delta_scale, cudaStream_t stream) {
     rms::Args a;
+    a.delta_scale = delta_scale;
     a.x = x, a.delta = delta, a.n_parts = n_parts, a.part_stride = part_stride, a.delta_bias = delta_bias, a.weight = weight;
     a.rows = rows, a.out = out, a.width = width, a.eps = eps;
     a.cs = width >= 2048 ? 8 : (width >= 1024 ? 4 : 1);
@@ -441,18 +443,24 @@ static int rmsnorm_dispatch(float *x, const TD *delta, int n_parts, long long pa
 
 // delta: null, or [n_parts][rows of x][width] (part_stride elements between parts) whose parts
 // are summed in order, plus delta_bias[width] if given.
-LGML_API int lgml_rmsnorm(float *x, const void *delta, int delta_dtype, int n_parts, long long part_stride, const float *delta_bias,
+LGML_API int lgml_rmsnorm_scaled(float *x, const void *delta, int delta_dtype, int n_parts, long long part_stride, const float *delta_bias,
                           const float *weight, const int *rows, void *out, int out_dtype, int n_rows, int width, float eps,
-                          cudaStream_t stream) {
+                          float delta_scale, cudaStream_t stream) {
     LGML_REQUIRE(n_rows >= 0 && width > 0, "rmsnorm: bad sizes");
     LGML_REQUIRE(out_dtype == LGML_F32 || out_dtype == LGML_BF16, "rmsnorm: unknown output type %d", out_dtype);
     LGML_REQUIRE(delta == nullptr || n_parts >= 1, "rmsnorm: a delta has at least one part");
     if (n_rows == 0) return 0;
     if (delta == nullptr || delta_dtype == LGML_F32)
-        return rmsnorm_dispatch<float>(x, (const float *)delta, n_parts, part_stride, delta_bias, weight, rows, out, out_dtype, n_rows, width, eps, stream);
+        return rmsnorm_dispatch<float>(x, (const float *)delta, n_parts, part_stride, delta_bias, weight, rows, out, out_dtype, n_rows, width, eps, delta_scale, stream);
     if (delta_dtype == LGML_BF16)
-        return rmsnorm_dispatch<__nv_bfloat16>(x, (const __nv_bfloat16 *)delta, n_parts, part_stride, delta_bias, weight, rows, out, out_dtype, n_rows, width, eps, stream);
+        return rmsnorm_dispatch<__nv_bfloat16>(x, (const __nv_bfloat16 *)delta, n_parts, part_stride, delta_bias, weight, rows, out, out_dtype, n_rows, width, eps, delta_scale, stream);
     LGML_FAIL("rmsnorm: unknown delta type %d", delta_dtype);
+}
+
+LGML_API int lgml_rmsnorm(float *x, const void *delta, int delta_dtype, int n_parts, long long part_stride, const float *delta_bias,
+                          const float *weight, const int *rows, void *out, int out_dtype, int n_rows, int width, float eps,
+                          cudaStream_t stream) {
+    return lgml_rmsnorm_scaled(x, delta, delta_dtype, n_parts, part_stride, delta_bias, weight, rows, out, out_dtype, n_rows, width, eps, 1.0f, stream);
 }
 
 // ---------------------------------------------------------------------------------------

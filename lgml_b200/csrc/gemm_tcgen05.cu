@@ -1101,11 +1101,11 @@ LGML_API int lgml_gemm_tcgen05_glu_clamped(const void *x, const void *w, void *y
 LGML_API int lgml_gemm_tcgen05_grouped(const void *x, const void *w, void *y, int y_f32, int max_tiles, int N, int K, int n_groups, int ldy,
                                        const int *group, int swiglu, int *status, cudaStream_t stream) {
     LGML_REQUIRE(max_tiles > 0 && N > 0 && K > 0 && n_groups > 0 && group != nullptr, "gemm_tcgen05_grouped: bad sizes");
-    LGML_REQUIRE(swiglu == 0 || swiglu == 1, "gemm_tcgen05_grouped: unknown epilogue %d", swiglu);
-    LGML_REQUIRE(swiglu == 0 || N % 2 == 0, "gemm_tcgen05_grouped: the gated epilogue needs an even N");
+    LGML_REQUIRE(swiglu >= 0 && swiglu <= 2, "gemm_tcgen05_grouped: unknown epilogue %d", swiglu);
+    LGML_REQUIRE(swiglu != 1 || N % 2 == 0, "gemm_tcgen05_grouped: the gated epilogue needs an even N");
     LGML_REQUIRE(K % 8 == 0, "gemm_tcgen05_grouped: K = %d must be a multiple of 8 elements (16 bytes) for TMA", K);
     LGML_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_tcgen05_grouped: operands must be 16-byte aligned for TMA");
-    LGML_REQUIRE(ldy >= (swiglu ? N / 2 : N), "gemm_tcgen05_grouped: the output's rows are too short");
+    LGML_REQUIRE(ldy >= (swiglu == 1 ? N / 2 : N), "gemm_tcgen05_grouped: the output's rows are too short");
     Params p;
     p.k_blocks = (K + BK - 1) / BK;
     p.kb_per_split = p.k_blocks;

@@ -23,11 +23,14 @@ namespace {
 
 template <typename T>
 __global__ void __launch_bounds__(128) moe_router_kernel(const T *__restrict__ h, int ldh, const float *__restrict__ wr, const float *__restrict__ br,
-                                                         int *__restrict__ ids, float *__restrict__ wts, int E, int X, int top) {
+                                                         int *__restrict__ ids, float *__restrict__ wts, int E, int X, int top, int mode,
+                                                         float route_scale, int n_extra, float *__restrict__ extra) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ __align__(16) float rsm[];        // X logits, then the token's row (E floats, from a 16-byte boundary)
-    float *z = rsm, *hs = rsm + ((X + 3) & ~3);
+    // X choice values (+ n_extra logits of rows that are no experts), X scores (mode 1), then the token's row (E floats, from a 16-byte boundary)
+    extern __shared__ __align__(16) float rsm[];
+    const int zn = (X + n_extra + 3) & ~3;
+    float *z = rsm, *sc = rsm + zn, *hs = rsm + 2 * zn;
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const T *row = h + (size_t)t * ldh;
@@ -35,7 +38,7 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const T *__restrict__ h
     __syncthreads();
     // one order of summation whatever the batch: lane l takes elements 4 l .. 4 l + 3 of every run of 128, then the warp's tree
     const bool vec = (E % 4 == 0) && ((reinterpret_cast<uintptr_t>(wr) & 15) == 0);
-    for (int e = warp; e < X; e += n_warps) {
+    for (int e = warp; e < X + n_extra; e += n_warps) {
         const float *w = wr + (size_t)e * E;
         float dot = 0.f;
         if (vec) {
@@ -48,7 +51,19 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const T *__restrict__ h
             for (int k = lane; k < E; k += 32) dot = fmaf(hs[k], w[k], dot);
         }
         dot = warp_sum(dot);
-        if (lane == 0) z[e] = dot + (br ? br[e] : 0.f);
+        if (lane == 0) {
+            if (e >= X) {
+                // rows behind the experts': a gate of the token (sigmoid of its logit), for the caller
+                extra[(size_t)t * n_extra + (e - X)] = 1.0f / (1.0f + expf(-dot));
+            } else if (mode == 1) {
+                // scores are sigmoids; the bias only corrects the choice, the weights use the plain scores
+                const float sg = 1.0f / (1.0f + expf(-dot));
+                sc[e] = sg;
+                z[e] = sg + (br ? br[e] : 0.f);
+            } else {
+                z[e] = dot + (br ? br[e] : 0.f);
+            }
+        }
     }
     __syncthreads();
     if (warp != 0) return;
@@ -68,7 +83,7 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const T *__restrict__ h
         }
         if (at == 0x7fffffff) at = 0;               // every logit was -inf or NaN
         if (s == 0) zmax = best;
-        const float p = expf(best - zmax);
+        const float p = mode == 1 ? sc[at] : expf(best - zmax);
         sum += p;
         if (lane == 0) {
             ids[(size_t)t * top + s] = at;
@@ -77,7 +92,8 @@ __global__ void __launch_bounds__(128) moe_router_kernel(const T *__restrict__ h
         }
         __syncwarp();
     }
-    const float inv = 1.0f / sum;
+    // mode 0: softmax over the chosen logits; mode 1: the chosen scores over their sum (+ 1e-20), times a constant
+    const float inv = mode == 1 ? route_scale / (sum + 1e-20f) : 1.0f / sum;
     for (int s = lane; s < top; s += 32) wts[(size_t)t * top + s] *= inv;
 }
 
@@ -108,7 +124,7 @@ __device__ __forceinline__ void rows_dot_bf16(const __nv_bfloat16 *const (&rows)
 constexpr int GU_WARPS = 4, GU_PER_WARP = 4;
 template <typename T>
 __global__ void __launch_bounds__(GU_WARPS * 32) moe_gate_up_kernel(const T *__restrict__ h, int ldh, const int *__restrict__ ids, const T *__restrict__ wgu,
-                                                                    T *__restrict__ act, int E, int F, int X, int top) {
+                                                                    T *__restrict__ act, int E, int F, int X, int top, int plain) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float hs[];       // the token's row
@@ -120,6 +136,33 @@ __global__ void __launch_bounds__(GU_WARPS * 32) moe_gate_up_kernel(const T *__r
     __syncthreads();
     const int f0 = (blockIdx.y * GU_WARPS + warp) * GU_PER_WARP;
     if (f0 >= F) return;
+    if (plain) {
+        // experts without a gate: wgu is [X, F, E] and act = relu(W_up h)^2
+        const T *we = wgu + (size_t)e * F * E;
+        if (sizeof(T) == 2 && (E % 8 == 0) && (reinterpret_cast<uintptr_t>(wgu) & 15) == 0) {
+            const __nv_bfloat16 *rows[GU_PER_WARP];
+#pragma unroll
+            for (int i = 0; i < GU_PER_WARP; ++i) rows[i] = reinterpret_cast<const __nv_bfloat16 *>(we) + (size_t)min(f0 + i, F - 1) * E;
+            float r[GU_PER_WARP];
+            rows_dot_bf16<GU_PER_WARP>(rows, hs, E, lane, r);
+            if (lane == 0)
+#pragma unroll
+                for (int i = 0; i < GU_PER_WARP; ++i)
+                    if (f0 + i < F) {
+                        const float a = fmaxf(r[i], 0.f);
+                        act[(size_t)row * F + f0 + i] = from_f32<T>(a * a);
+                    }
+            return;
+        }
+        for (int f = f0; f < f0 + GU_PER_WARP && f < F; ++f) {
+            const T *u_row = we + (size_t)f * E;
+            float u = 0.f;
+            for (int k = lane; k < E; k += 32) u = fmaf(hs[k], to_f32(u_row[k]), u);
+            u = fmaxf(warp_sum(u), 0.f);
+            if (lane == 0) act[(size_t)row * F + f] = from_f32<T>(u * u);
+        }
+        return;
+    }
     // expert e's rows: gate of feature f at row 2 f, its up at row 2 f + 1
     const T *we = wgu + (size_t)e * 2 * F * E;
     if (sizeof(T) == 2 && (E % 8 == 0) && (reinterpret_cast<uintptr_t>(wgu) & 15) == 0) {
@@ -157,7 +200,8 @@ __global__ void __launch_bounds__(GU_WARPS * 32) moe_gate_up_kernel(const T *__r
 constexpr int DN_WARPS = 4, DN_PER_WARP = 4;
 template <typename T>
 __global__ void __launch_bounds__(DN_WARPS * 32) moe_down_kernel(const T *__restrict__ act, const int *__restrict__ ids, const float *__restrict__ wts,
-                                                                 const T *__restrict__ wd, float *__restrict__ out, int E, int F, int X, int top) {
+                                                                 const T *__restrict__ wd, float *__restrict__ out, int E, int F, int X, int top,
+                                                                 const float *__restrict__ also, const float *__restrict__ also_w) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float as[];       // top rows of F
@@ -193,10 +237,15 @@ __global__ void __launch_bounds__(DN_WARPS * 32) moe_down_kernel(const T *__rest
 #pragma unroll
         for (int i = 0; i < DN_PER_WARP; ++i) total[i] = fmaf(w, r[i], total[i]);
     }
+    // `also`: a term every token gets beside its chosen experts (a shared expert's output), times the token's own weight
     if (lane == 0)
 #pragma unroll
         for (int i = 0; i < DN_PER_WARP; ++i)
-            if (j0 + i < E) out[(size_t)t * E + j0 + i] = total[i];
+            if (j0 + i < E) {
+                float v = total[i];
+                if (also) v = fmaf(act_load(also_w + t), act_load(also + (size_t)t * E + j0 + i), v);
+                out[(size_t)t * E + j0 + i] = v;
+            }
 }
 
 template <typename K>
@@ -210,26 +259,39 @@ static int need_smem(K kernel, size_t smem, const char *who) {
 }  // namespace
 
 // h: [n, ldh] in the compute type; wr: float32 [X, E]; br: float32 [X] or null; ids int32 / wts float32 [n, top]
-LGML_API int lgml_moe_router(const void *h, int dtype, int ldh, const float *wr, const float *br, int *ids, float *wts, int n_tokens, int E, int X,
-                             int top, cudaStream_t stream) {
+//   mode 0: the chosen by the largest logits + br, weights = softmax over the chosen logits
+//   mode 1: scores = sigmoid(logits), the chosen by the largest score + br, weights = score / (sum of the chosen scores + 1e-20) * route_scale
+//   wr holds n_extra more rows behind the experts': extra[n, n_extra] = sigmoid of their logits
+LGML_API int lgml_moe_router_mode(const void *h, int dtype, int ldh, const float *wr, const float *br, int *ids, float *wts, int n_tokens, int E, int X,
+                                  int top, int mode, float route_scale, int n_extra, float *extra, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && E > 0 && X > 0 && top > 0 && top <= X, "moe_router: bad sizes (%d experts, %d chosen)", X, top);
     LGML_REQUIRE(X <= 8192, "moe_router: at most 8192 experts");
+    LGML_REQUIRE(mode == 0 || mode == 1, "moe_router: unknown mode %d", mode);
+    LGML_REQUIRE(n_extra >= 0 && n_extra <= 64 && (n_extra == 0 || extra != nullptr), "moe_router: bad extra rows");
     if (n_tokens == 0) return 0;
-    const size_t smem = sizeof(float) * ((size_t)((X + 3) & ~3) + (size_t)E);
+    const size_t smem = sizeof(float) * (2 * (size_t)((X + n_extra + 3) & ~3) + (size_t)E);
     LGML_REQUIRE(smem <= 200 * 1024, "moe_router: %d experts and rows of %d do not fit shared memory", X, E);
     if (need_smem(moe_router_kernel<float>, smem, "moe_router") || need_smem(moe_router_kernel<__nv_bfloat16>, smem, "moe_router")) return -1;
     if (dtype == LGML_F32)
-        lgml_launch(moe_router_kernel<float>, n_tokens, 128, smem, stream, (const float *)h, ldh, wr, br, ids, wts, E, X, top);
+        lgml_launch(moe_router_kernel<float>, n_tokens, 128, smem, stream, (const float *)h, ldh, wr, br, ids, wts, E, X, top, mode, route_scale, n_extra, extra);
     else if (dtype == LGML_BF16)
-        lgml_launch(moe_router_kernel<__nv_bfloat16>, n_tokens, 128, smem, stream, (const __nv_bfloat16 *)h, ldh, wr, br, ids, wts, E, X, top);
+        lgml_launch(moe_router_kernel<__nv_bfloat16>, n_tokens, 128, smem, stream, (const __nv_bfloat16 *)h, ldh, wr, br, ids, wts, E, X, top, mode,
+                    route_scale, n_extra, extra);
     else
         LGML_FAIL("moe_router: unknown type %d", dtype);
     return lgml_launch_status("moe_router");
 }
 
+LGML_API int lgml_moe_router(const void *h, int dtype, int ldh, const float *wr, const float *br, int *ids, float *wts, int n_tokens, int E, int X,
+                             int top, cudaStream_t stream) {
+    return lgml_moe_router_mode(h, dtype, ldh, wr, br, ids, wts, n_tokens, E, X, top, 0, 1.0f, 0, nullptr, stream);
+}
+
 // The row form: act [n top, F] in the compute type (scratch of the caller), out float32 [n, E].
-LGML_API int lgml_moe_experts_rows(const void *h, int dtype, int ldh, const int *ids, const float *wts, const void *wgu, const void *wd,
-                                   void *act, float *out, int n_tokens, int E, int F, int X, int top, cudaStream_t stream) {
+// plain = 1: experts without a gate (wgu is [X, F, E], act = relu(W_up h)^2).  also / also_w: float32 [n, E] and [n], out += also_w[t] also[t] (or null).
+LGML_API int lgml_moe_experts_rows_form(const void *h, int dtype, int ldh, const int *ids, const float *wts, const void *wgu, const void *wd,
+                                        void *act, float *out, int n_tokens, int E, int F, int X, int top, int plain, const float *also,
+                                        const float *also_w, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && E > 0 && F > 0 && X > 0 && top > 0, "moe_experts_rows: bad sizes");
     if (n_tokens == 0) return 0;
     const size_t smem_gu = sizeof(float) * (size_t)E, smem_dn = sizeof(float) * (size_t)top * F;
@@ -239,20 +301,26 @@ LGML_API int lgml_moe_experts_rows(const void *h, int dtype, int ldh, const int 
     if (dtype == LGML_F32) {
         if (need_smem(moe_gate_up_kernel<float>, smem_gu, "moe_experts_rows") || need_smem(moe_down_kernel<float>, smem_dn, "moe_experts_rows")) return -1;
         lgml_launch(moe_gate_up_kernel<float>, grid_gu, GU_WARPS * 32, smem_gu, stream, (const float *)h, ldh, ids, (const float *)wgu, (float *)act, E, F, X,
-                    top);
-        lgml_launch(moe_down_kernel<float>, grid_dn, DN_WARPS * 32, smem_dn, stream, (const float *)act, ids, wts, (const float *)wd, out, E, F, X, top);
+                    top, plain);
+        lgml_launch(moe_down_kernel<float>, grid_dn, DN_WARPS * 32, smem_dn, stream, (const float *)act, ids, wts, (const float *)wd, out, E, F, X, top,
+                    also, also_w);
     } else if (dtype == LGML_BF16) {
         if (need_smem(moe_gate_up_kernel<__nv_bfloat16>, smem_gu, "moe_experts_rows") ||
             need_smem(moe_down_kernel<__nv_bfloat16>, smem_dn, "moe_experts_rows"))
             return -1;
         lgml_launch(moe_gate_up_kernel<__nv_bfloat16>, grid_gu, GU_WARPS * 32, smem_gu, stream, (const __nv_bfloat16 *)h, ldh, ids,
-                    (const __nv_bfloat16 *)wgu, (__nv_bfloat16 *)act, E, F, X, top);
+                    (const __nv_bfloat16 *)wgu, (__nv_bfloat16 *)act, E, F, X, top, plain);
         lgml_launch(moe_down_kernel<__nv_bfloat16>, grid_dn, DN_WARPS * 32, smem_dn, stream, (const __nv_bfloat16 *)act, ids, wts,
-                    (const __nv_bfloat16 *)wd, out, E, F, X, top);
+                    (const __nv_bfloat16 *)wd, out, E, F, X, top, also, also_w);
     } else {
         LGML_FAIL("moe_experts_rows: unknown type %d", dtype);
     }
     return lgml_launch_status("moe_experts_rows");
+}
+
+LGML_API int lgml_moe_experts_rows(const void *h, int dtype, int ldh, const int *ids, const float *wts, const void *wgu, const void *wd,
+                                   void *act, float *out, int n_tokens, int E, int F, int X, int top, cudaStream_t stream) {
+    return lgml_moe_experts_rows_form(h, dtype, ldh, ids, wts, wgu, wd, act, out, n_tokens, E, F, X, top, 0, nullptr, nullptr, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -517,10 +585,11 @@ __global__ void __launch_bounds__(128) moe_gather_rows_kernel(const __nv_bfloat1
 }
 
 __global__ void __launch_bounds__(256) moe_weighted_sum_kernel(const float *__restrict__ y, const int *__restrict__ pos, const float *__restrict__ wts,
-                                                               float *__restrict__ out, int n_tokens, int E, int top) {
+                                                               float *__restrict__ out, int n_tokens, int E, int top,
+                                                               const float *__restrict__ also, const float *__restrict__ also_w) {
     pdl_trigger();
     pdl_wait();
-    if (E % 4 == 0 && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+    if (E % 4 == 0 && ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(also)) & 15) == 0) {
         const int quads = E / 4;
         const size_t total = (size_t)n_tokens * quads;
         for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -529,6 +598,11 @@ __global__ void __launch_bounds__(256) moe_weighted_sum_kernel(const float *__re
             for (int k = 0; k < top; ++k) {
                 const float w = act_load(wts + t * top + k);
                 const float4 v = act_load(reinterpret_cast<const float4 *>(y + (size_t)act_load(pos + t * top + k) * E + j));
+                s.x = fmaf(w, v.x, s.x), s.y = fmaf(w, v.y, s.y), s.z = fmaf(w, v.z, s.z), s.w = fmaf(w, v.w, s.w);
+            }
+            if (also) {
+                const float w = act_load(also_w + t);
+                const float4 v = act_load(reinterpret_cast<const float4 *>(also + t * E + j));
                 s.x = fmaf(w, v.x, s.x), s.y = fmaf(w, v.y, s.y), s.z = fmaf(w, v.z, s.z), s.w = fmaf(w, v.w, s.w);
             }
             *reinterpret_cast<float4 *>(out + t * E + j) = s;
@@ -540,6 +614,7 @@ __global__ void __launch_bounds__(256) moe_weighted_sum_kernel(const float *__re
         const size_t t = i / E, j = i - t * E;
         float s = 0.f;
         for (int k = 0; k < top; ++k) s = fmaf(act_load(wts + t * top + k), act_load(y + (size_t)act_load(pos + t * top + k) * E + j), s);
+        if (also) s = fmaf(act_load(also_w + t), act_load(also + i), s);
         out[i] = s;
     }
 }
@@ -567,11 +642,16 @@ LGML_API int lgml_moe_gather_rows(const void *h, int ldh, const int *rows, const
     return lgml_launch_status("moe_gather_rows");
 }
 
-LGML_API int lgml_moe_weighted_sum(const float *y, const int *pos, const float *wts, float *out, int n_tokens, int E, int top, cudaStream_t stream) {
+LGML_API int lgml_moe_weighted_sum_also(const float *y, const int *pos, const float *wts, float *out, int n_tokens, int E, int top, const float *also,
+                                        const float *also_w, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && E > 0 && top > 0, "moe_weighted_sum: bad sizes");
     if (n_tokens == 0) return 0;
     const size_t total = (size_t)n_tokens * E;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-    lgml_launch(moe_weighted_sum_kernel, blocks, 256, 0, stream, y, pos, wts, out, n_tokens, E, top);
+    lgml_launch(moe_weighted_sum_kernel, blocks, 256, 0, stream, y, pos, wts, out, n_tokens, E, top, also, also_w);
     return lgml_launch_status("moe_weighted_sum");
+}
+
+LGML_API int lgml_moe_weighted_sum(const float *y, const int *pos, const float *wts, float *out, int n_tokens, int E, int top, cudaStream_t stream) {
+    return lgml_moe_weighted_sum_also(y, pos, wts, out, n_tokens, E, top, nullptr, nullptr, stream);
 }

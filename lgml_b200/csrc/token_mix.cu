@@ -1,0 +1,409 @@
+// Mechanisms that carry something from one token of a request to the next, or add something of
+// the token itself, around the mixers:
+//
+//   token_shift    y_t = h_t + (h_(t-1) - h_t) mu, per channel; h_(-1) = 0; the last h of a portion
+//                  waits in the request's state slot for the next portion
+//   mingru_scan    S_t = (1 - z_t) S_(t-1) + z_t c_t per channel, z = sigmoid(a), c = u + 1/2 (u >= 0)
+//                  or sigmoid(u) (u < 0); out_t = S_t silu(g_t); S lives in the state slot
+//   mingru_chunks  the same recurrence for long portions in three passes: every chunk of tokens gives
+//                  (prod (1 - z), the scan from zero), the chunks' ends are chained, then every chunk
+//                  runs again from its true start
+//   token_side     x += m delta;  y = W_p (gelu_tanh(W_g x) e_token);  x += m y / rms(y) w
+//
+// Everything here is float32 arithmetic in both compute types; only the results that feed a
+// matrix product (token_shift's y, the scan's out) are stored in the compute type.
+#include <math.h>
+
+#include "common.cuh"
+
+LGML_DEFINE_LAST_ERROR(lgml_token_mix)
+
+namespace {
+
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+template <typename TO> __device__ __forceinline__ void store4(TO *p, const float (&v)[4]);
+template <> __device__ __forceinline__ void store4<float>(float *p, const float (&v)[4]) {
+    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16 *p, const float (&v)[4]) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+    float2 raw;
+    raw.x = *reinterpret_cast<float *>(&lo), raw.y = *reinterpret_cast<float *>(&hi);
+    *reinterpret_cast<float2 *>(p) = raw;
+}
+
+// h float32 [n, W]; out [n, W]; state float32 rows of `state_ld` floats, one per slot, W of them used.
+// A thread takes four channels of one token (one when W is no multiple of 4).  The thread of a
+// request's first token of this step reads the slot and then writes the portion's last h into it:
+// nobody else touches those four floats.
+template <typename TO, int V>
+__global__ void __launch_bounds__(256) token_shift_kernel(const float *__restrict__ h, const float *__restrict__ mu, float *__restrict__ state,
+                                                          long long state_ld, const int *__restrict__ seq_of_token, const int *__restrict__ seq_start,
+                                                          const int *__restrict__ slots, TO *__restrict__ out, int n, int W) {
+    pdl_trigger();
+    pdl_wait();
+    const int per_row = W / V;
+    const size_t total = (size_t)n * per_row;
+    for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(it / per_row), c = (int)(it - (size_t)t * per_row) * V;
+        const int s = seq_of_token[t];
+        const int t0 = seq_start[s];
+        float cur[4], prev[4], m[4], y[4];
+        if (V == 4) {
+            const float4 a = act_load(reinterpret_cast<const float4 *>(h + (size_t)t * W + c));
+            cur[0] = a.x, cur[1] = a.y, cur[2] = a.z, cur[3] = a.w;
+            const float4 b = __ldg(reinterpret_cast<const float4 *>(mu + c));
+            m[0] = b.x, m[1] = b.y, m[2] = b.z, m[3] = b.w;
+        } else {
+            cur[0] = act_load(h + (size_t)t * W + c);
+            m[0] = __ldg(mu + c);
+        }
+        if (t == t0) {
+            float *st = state + (size_t)slots[s] * state_ld + c;
+            const float *last = h + (size_t)(seq_start[s + 1] - 1) * W + c;
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                prev[e] = act_load(st + e);
+                st[e] = act_load(last + e);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < V; ++e) prev[e] = act_load(h + (size_t)(t - 1) * W + c + e);
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) y[e] = fmaf(prev[e] - cur[e], m[e], cur[e]);
+        if (V == 4) store4<TO>(out + (size_t)t * W + c, y);
+        else out[(size_t)t * W + c] = from_f32<TO>(y[0]);
+    }
+}
+
+// candidate of the recurrence: u + 1/2 where u >= 0, sigmoid(u) where u < 0 (continuous, positive)
+__device__ __forceinline__ float mingru_candidate(float u) { return u >= 0.f ? u + 0.5f : sigmoidf_(u); }
+
+// proj float32 [n, ld]: per token z-logits at column 0, u at W, g at 2 W.  A thread owns one channel of
+// one request and walks its tokens in order; the loads of AHEAD tokens are in flight at a time.
+template <typename TO>
+__global__ void __launch_bounds__(128) mingru_scan_kernel(const float *__restrict__ proj, int ld, float *__restrict__ state, long long state_ld,
+                                                          const int *__restrict__ seq_start, const int *__restrict__ slots, TO *__restrict__ out,
+                                                          int W) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int AHEAD = 8;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
+    if (c >= W) return;
+    const int t0 = seq_start[s], t1 = seq_start[s + 1];
+    float *st = state + (size_t)slots[s] * state_ld + c;
+    float S = act_load(st);
+    for (int t = t0; t < t1; t += AHEAD) {
+        float a[AHEAD], u[AHEAD], g[AHEAD];
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i)
+            if (t + i < t1) {
+                const float *row = proj + (size_t)(t + i) * ld + c;
+                a[i] = act_load(row), u[i] = act_load(row + W), g[i] = act_load(row + 2 * W);
+            }
+#pragma unroll
+        for (int i = 0; i < AHEAD; ++i)
+            if (t + i < t1) {
+                const float z = sigmoidf_(a[i]);
+                S = fmaf(z, mingru_candidate(u[i]) - S, S);         // (1 - z) S + z c
+                out[(size_t)(t + i) * W + c] = from_f32<TO>(S * g[i] * sigmoidf_(g[i]));
+            }
+    }
+    *st = S;
+}
+
+// The three passes for long portions.  Chunks of CHUNK tokens, counted from the start of each request's
+// portion; `chunk_start[s]` is the index of request s's first chunk in the (A, B) arrays.
+//   pass 1: per (chunk, channel): A = prod (1 - z), B = the scan's end from S = 0
+//   pass 2: per (request, channel): S at the start of every chunk (written over B), and the slot's new state
+//   pass 3: per (chunk, channel): the scan from its start, out = S silu(g)
+constexpr int CHUNK = 64;
+__global__ void __launch_bounds__(128) mingru_chunk_ends_kernel(const float *__restrict__ proj, int ld, const int *__restrict__ chunks,
+                                                                float *__restrict__ A, float *__restrict__ B, int W) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, k = blockIdx.y;
+    if (c >= W) return;
+    const int t0 = chunks[2 * k], t1 = chunks[2 * k + 1];
+    float a = 1.f, S = 0.f;
+    for (int t = t0; t < t1; t += 8) {
+        float zl[8], u[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (t + i < t1) {
+                const float *row = proj + (size_t)(t + i) * ld + c;
+                zl[i] = act_load(row), u[i] = act_load(row + W);
+            }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (t + i < t1) {
+                const float z = sigmoidf_(zl[i]);
+                S = fmaf(z, mingru_candidate(u[i]) - S, S);
+                a *= 1.f - z;
+            }
+    }
+    A[(size_t)k * W + c] = a, B[(size_t)k * W + c] = S;
+}
+
+__global__ void __launch_bounds__(128) mingru_chain_kernel(const float *__restrict__ A, float *__restrict__ B, const int *__restrict__ chunk_start,
+                                                           float *__restrict__ state, long long state_ld, const int *__restrict__ slots, int W) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
+    if (c >= W) return;
+    float *st = state + (size_t)slots[s] * state_ld + c;
+    float S = act_load(st);
+    for (int k = chunk_start[s]; k < chunk_start[s + 1]; ++k) {
+        const float a = act_load(A + (size_t)k * W + c), b = act_load(B + (size_t)k * W + c);
+        B[(size_t)k * W + c] = S;                   // the state this chunk starts from
+        S = fmaf(a, S, b);
+    }
+    *st = S;
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(128) mingru_chunk_scan_kernel(const float *__restrict__ proj, int ld, const int *__restrict__ chunks,
+                                                                const float *__restrict__ S0, TO *__restrict__ out, int W) {
+    pdl_trigger();
+    pdl_wait();
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, k = blockIdx.y;
+    if (c >= W) return;
+    const int t0 = chunks[2 * k], t1 = chunks[2 * k + 1];
+    float S = act_load(S0 + (size_t)k * W + c);
+    for (int t = t0; t < t1; t += 8) {
+        float zl[8], u[8], g[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (t + i < t1) {
+                const float *row = proj + (size_t)(t + i) * ld + c;
+                zl[i] = act_load(row), u[i] = act_load(row + W), g[i] = act_load(row + 2 * W);
+            }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (t + i < t1) {
+                const float z = sigmoidf_(zl[i]);
+                S = fmaf(z, mingru_candidate(u[i]) - S, S);
+                out[(size_t)(t + i) * W + c] = from_f32<TO>(S * g[i] * sigmoidf_(g[i]));
+            }
+    }
+}
+
+__device__ __forceinline__ float gelu_tanh(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+
+// One block per token.  x float32 [n, W] in place; delta float32 [parts, n, W] or null (its parts added in
+// order, then its bias, the sum times delta_scale into x); table [vocab, ld_table] whose columns
+// col0 .. col0 + dim - 1 are this layer's; wg [dim, W], wp [W, dim] in T; norm_w float32 [W].
+template <typename T>
+__global__ void __launch_bounds__(256) token_side_kernel(float *__restrict__ x, const float *__restrict__ delta, int n_parts, long long part_stride,
+                                                         const float *__restrict__ delta_bias, float delta_scale, const int *__restrict__ token_ids,
+                                                         const T *__restrict__ table, int ld_table, int col0, int vocab, const T *__restrict__ wg,
+                                                         const T *__restrict__ wp, const float *__restrict__ norm_w, float eps, float out_scale,
+                                                         int W, int dim) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];         // x row [W], y [W], g [dim]
+    __shared__ float red[32];
+    float *xs = sm, *ys = sm + W, *gs = sm + 2 * W;
+    const int t = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    float *xr = x + (size_t)t * W;
+    for (int k = threadIdx.x; k < W; k += blockDim.x) {
+        float v = act_load(xr + k);
+        if (delta) {
+            float d = 0.f;
+            for (int p = 0; p < n_parts; ++p) d += act_load(delta + (size_t)p * part_stride + (size_t)t * W + k);
+            if (delta_bias) d += __ldg(delta_bias + k);
+            v = fmaf(delta_scale, d, v);
+        }
+        xs[k] = v;
+    }
+    __syncthreads();
+    int id = token_ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);           // the embedding kernel has flagged such an id
+    for (int j = warp; j < dim; j += n_warps) {
+        const T *w = wg + (size_t)j * W;
+        float dot = 0.f;
+        for (int k = lane; k < W; k += 32) dot = fmaf(xs[k], to_f32(w[k]), dot);
+        dot = warp_sum(dot);
+        if (lane == 0) gs[j] = gelu_tanh(dot) * to_f32(table[(size_t)id * ld_table + col0 + j]);
+    }
+    __syncthreads();
+    float ss = 0.f;
+    for (int k = threadIdx.x; k < W; k += blockDim.x) {
+        const T *w = wp + (size_t)k * dim;
+        float y = 0.f;
+        for (int j = 0; j < dim; ++j) y = fmaf(gs[j], to_f32(w[j]), y);
+        ys[k] = y;
+        ss = fmaf(y, y, ss);
+    }
+    ss = block_sum(ss, red);
+    const float inv = out_scale / sqrtf(ss / (float)W + eps);
+    for (int k = threadIdx.x; k < W; k += blockDim.x) xr[k] = fmaf(ys[k] * inv, __ldg(norm_w + k), xs[k]);
+}
+
+// The pieces of the same for many tokens, where the two small products run as the framework's matrix products:
+//   side_fold   x += m delta, and x in the compute type for the gate product (float32: x itself serves)
+//   side_gate   g = gelu_tanh(gate) e_token, in the compute type
+//   side_add    x += m y / rms(y) w, y float32
+template <typename TO>
+__global__ void __launch_bounds__(256) side_fold_kernel(float *__restrict__ x, const float *__restrict__ delta, int n_parts, long long part_stride,
+                                                        const float *__restrict__ delta_bias, float delta_scale, TO *__restrict__ xb, int n, int W) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t total = (size_t)n * W;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        float v = act_load(x + i);
+        if (delta) {
+            float d = 0.f;
+            for (int p = 0; p < n_parts; ++p) d += act_load(delta + (size_t)p * part_stride + i);
+            if (delta_bias) d += __ldg(delta_bias + (i % W));
+            v = fmaf(delta_scale, d, v);
+            x[i] = v;
+        }
+        if (xb) xb[i] = from_f32<TO>(v);
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) side_gate_kernel(const float *__restrict__ gate, const int *__restrict__ token_ids, const T *__restrict__ table,
+                                                        int ld_table, int col0, int vocab, T *__restrict__ g, int n, int dim) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t total = (size_t)n * dim;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int t = (int)(i / dim), j = (int)(i - (size_t)t * dim);
+        int id = token_ids[t];
+        id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+        g[i] = from_f32<T>(gelu_tanh(act_load(gate + i)) * to_f32(table[(size_t)id * ld_table + col0 + j]));
+    }
+}
+
+__global__ void __launch_bounds__(256) side_add_kernel(float *__restrict__ x, const float *__restrict__ y, const float *__restrict__ norm_w, float eps,
+                                                       float out_scale, int W) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float red[32];
+    const int t = blockIdx.x;
+    const float *yr = y + (size_t)t * W;
+    float ss = 0.f;
+    for (int k = threadIdx.x; k < W; k += blockDim.x) {
+        const float v = act_load(yr + k);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float inv = out_scale / sqrtf(ss / (float)W + eps);
+    float *xr = x + (size_t)t * W;
+    for (int k = threadIdx.x; k < W; k += blockDim.x) xr[k] = fmaf(act_load(yr + k) * inv, __ldg(norm_w + k), act_load(xr + k));
+}
+
+static int grid_for(size_t items, int threads) {
+    const size_t blocks = (items + threads - 1) / threads;
+    return (int)(blocks < 148 * 16 ? (blocks ? blocks : 1) : 148 * 16);
+}
+}  // namespace
+
+LGML_API int lgml_token_shift(const float *h, const float *mu, float *state, long long state_ld, const int *seq_of_token, const int *seq_start,
+                              const int *slots, void *out, int out_dtype, int n_tokens, int W, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && W > 0 && state_ld >= W, "token_shift: bad sizes");
+    if (n_tokens == 0) return 0;
+    const bool vec = W % 4 == 0 && state_ld % 4 == 0 && ((((uintptr_t)h | (uintptr_t)mu | (uintptr_t)state) & 15) == 0) && (((uintptr_t)out & 7) == 0);
+    const int grid = grid_for((size_t)n_tokens * (vec ? W / 4 : W), 256);
+#define LGML_TS(TO, V) lgml_launch(token_shift_kernel<TO, V>, grid, 256, 0, stream, h, mu, state, state_ld, seq_of_token, seq_start, slots, (TO *)out, n_tokens, W)
+    if (out_dtype == LGML_F32) { if (vec) LGML_TS(float, 4); else LGML_TS(float, 1); }
+    else if (out_dtype == LGML_BF16) { if (vec) LGML_TS(__nv_bfloat16, 4); else LGML_TS(__nv_bfloat16, 1); }
+    else LGML_FAIL("token_shift: unknown output type %d", out_dtype);
+#undef LGML_TS
+    return lgml_launch_status("token_shift");
+}
+
+LGML_API int lgml_mingru_scan(const float *proj, int ld, float *state, long long state_ld, const int *seq_start, const int *slots, void *out,
+                              int out_dtype, int n_seqs, int W, cudaStream_t stream) {
+    LGML_REQUIRE(n_seqs >= 0 && W > 0 && ld >= 3 * W && state_ld >= W, "mingru_scan: bad sizes");
+    LGML_REQUIRE(n_seqs <= 65535, "mingru_scan: too many requests");
+    if (n_seqs == 0) return 0;
+    dim3 grid((W + 127) / 128, n_seqs);
+    if (out_dtype == LGML_F32) lgml_launch(mingru_scan_kernel<float>, grid, 128, 0, stream, proj, ld, state, state_ld, seq_start, slots, (float *)out, W);
+    else if (out_dtype == LGML_BF16)
+        lgml_launch(mingru_scan_kernel<__nv_bfloat16>, grid, 128, 0, stream, proj, ld, state, state_ld, seq_start, slots, (__nv_bfloat16 *)out, W);
+    else LGML_FAIL("mingru_scan: unknown output type %d", out_dtype);
+    return lgml_launch_status("mingru_scan");
+}
+
+// chunks int32 [n_chunks, 2]: first token row and the row past the last of each chunk, the chunks of a request in a
+// row; chunk_start int32 [n_seqs + 1]; ab float32 [2, n_chunks, W] scratch of the caller.
+LGML_API int lgml_mingru_chunks(const float *proj, int ld, float *state, long long state_ld, const int *chunks, const int *chunk_start, int n_chunks,
+                                const int *slots, float *ab, void *out, int out_dtype, int n_seqs, int W, cudaStream_t stream) {
+    LGML_REQUIRE(n_seqs >= 0 && n_chunks >= 0 && W > 0 && ld >= 3 * W && state_ld >= W, "mingru_chunks: bad sizes");
+    LGML_REQUIRE(n_seqs <= 65535 && n_chunks <= 65535, "mingru_chunks: too many requests or chunks");
+    if (n_seqs == 0 || n_chunks == 0) return 0;
+    float *A = ab, *B = ab + (size_t)n_chunks * W;
+    dim3 gc((W + 127) / 128, n_chunks), gs((W + 127) / 128, n_seqs);
+    lgml_launch(mingru_chunk_ends_kernel, gc, 128, 0, stream, proj, ld, chunks, A, B, W);
+    lgml_launch(mingru_chain_kernel, gs, 128, 0, stream, (const float *)A, B, chunk_start, state, state_ld, slots, W);
+    if (out_dtype == LGML_F32) lgml_launch(mingru_chunk_scan_kernel<float>, gc, 128, 0, stream, proj, ld, chunks, (const float *)B, (float *)out, W);
+    else if (out_dtype == LGML_BF16)
+        lgml_launch(mingru_chunk_scan_kernel<__nv_bfloat16>, gc, 128, 0, stream, proj, ld, chunks, (const float *)B, (__nv_bfloat16 *)out, W);
+    else LGML_FAIL("mingru_chunks: unknown output type %d", out_dtype);
+    return lgml_launch_status("mingru_chunks");
+}
+
+LGML_API int lgml_mingru_chunk_tokens(void) { return CHUNK; }
+
+LGML_API int lgml_token_side(float *x, const float *delta, int n_parts, long long part_stride, const float *delta_bias, float delta_scale,
+                             const int *token_ids, const void *table, int ld_table, int col0, int vocab, const void *wg, const void *wp,
+                             const float *norm_w, float eps, float out_scale, int dtype, int n_tokens, int W, int dim, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && W > 0 && dim > 0 && vocab > 0 && col0 >= 0 && col0 + dim <= ld_table, "token_side: bad sizes");
+    LGML_REQUIRE(delta == nullptr || n_parts >= 1, "token_side: a delta has at least one part");
+    if (n_tokens == 0) return 0;
+    const size_t smem = sizeof(float) * (2 * (size_t)W + dim);
+    LGML_REQUIRE(smem <= 200 * 1024, "token_side: rows of %d and %d entries do not fit shared memory", W, dim);
+#define LGML_SIDE(T)                                                                                                                         \
+    do {                                                                                                                                     \
+        if (smem > 48 * 1024 && cudaFuncSetAttribute(token_side_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+            LGML_FAIL("token_side: cannot have %zu bytes of shared memory", smem);                                                           \
+        lgml_launch(token_side_kernel<T>, n_tokens, 256, smem, stream, x, delta, n_parts, part_stride, delta_bias, delta_scale, token_ids,    \
+                    (const T *)table, ld_table, col0, vocab, (const T *)wg, (const T *)wp, norm_w, eps, out_scale, W, dim);                   \
+    } while (0)
+    if (dtype == LGML_F32) LGML_SIDE(float);
+    else if (dtype == LGML_BF16) LGML_SIDE(__nv_bfloat16);
+    else LGML_FAIL("token_side: unknown type %d", dtype);
+#undef LGML_SIDE
+    return lgml_launch_status("token_side");
+}
+
+LGML_API int lgml_side_fold(float *x, const float *delta, int n_parts, long long part_stride, const float *delta_bias, float delta_scale, void *xb,
+                            int xb_dtype, int n_tokens, int W, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && W > 0, "side_fold: bad sizes");
+    LGML_REQUIRE(delta == nullptr || n_parts >= 1, "side_fold: a delta has at least one part");
+    if (n_tokens == 0 || (delta == nullptr && xb == nullptr)) return 0;
+    const int grid = grid_for((size_t)n_tokens * W, 256);
+    if (xb == nullptr || xb_dtype == LGML_F32)
+        lgml_launch(side_fold_kernel<float>, grid, 256, 0, stream, x, delta, n_parts, part_stride, delta_bias, delta_scale, (float *)xb, n_tokens, W);
+    else if (xb_dtype == LGML_BF16)
+        lgml_launch(side_fold_kernel<__nv_bfloat16>, grid, 256, 0, stream, x, delta, n_parts, part_stride, delta_bias, delta_scale, (__nv_bfloat16 *)xb,
+                    n_tokens, W);
+    else LGML_FAIL("side_fold: unknown type %d", xb_dtype);
+    return lgml_launch_status("side_fold");
+}
+
+LGML_API int lgml_side_gate(const float *gate, const int *token_ids, const void *table, int ld_table, int col0, int vocab, void *g, int dtype,
+                            int n_tokens, int dim, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && dim > 0 && vocab > 0 && col0 >= 0 && col0 + dim <= ld_table, "side_gate: bad sizes");
+    if (n_tokens == 0) return 0;
+    const int grid = grid_for((size_t)n_tokens * dim, 256);
+    if (dtype == LGML_F32) lgml_launch(side_gate_kernel<float>, grid, 256, 0, stream, gate, token_ids, (const float *)table, ld_table, col0, vocab, (float *)g, n_tokens, dim);
+    else if (dtype == LGML_BF16)
+        lgml_launch(side_gate_kernel<__nv_bfloat16>, grid, 256, 0, stream, gate, token_ids, (const __nv_bfloat16 *)table, ld_table, col0, vocab,
+                    (__nv_bfloat16 *)g, n_tokens, dim);
+    else LGML_FAIL("side_gate: unknown type %d", dtype);
+    return lgml_launch_status("side_gate");
+}
+
+LGML_API int lgml_side_add(float *x, const float *y, const float *norm_w, float eps, float out_scale, int n_tokens, int W, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && W > 0, "side_add: bad sizes");
+    if (n_tokens == 0) return 0;
+    lgml_launch(side_add_kernel, n_tokens, 256, 0, stream, x, y, norm_w, eps, out_scale, W);
+    return lgml_launch_status("side_add");
+}

@@ -35,6 +35,21 @@ class CacheView:
     page_size: int = 0
 
 
+def cache_view_of(cm, owner: int, block_tables, writable: bool = True) -> CacheView:
+    """The cache of schedule entry ``owner`` as a step's requests see it: its pages with the step's block
+    table, its state slots, or both when the layer keeps both."""
+    view = CacheView(writable=False)
+    g = cm.group_of_layer.get(owner)
+    if g is not None:
+        grp = cm.groups[g]
+        view = CacheView(k=grp.k[owner], v=grp.v[owner], block_table=block_tables[g], writable=writable, page_size=cm.page_size)
+    sg = cm.state_group_of_layer.get(owner)
+    if sg is not None:
+        view.state = cm.state_groups[sg].state[owner]
+        view.writable = writable
+    return view
+
+
 class StepBatch:
     """Host lists -> one int32 buffer -> one copy -> device views.
 
@@ -161,21 +176,43 @@ class StepBatch:
             rows.sort(key=lambda r: -r[3])
             arr = np.asarray(rows, dtype=np.int32).reshape(-1, 4)
             arr[:, 3] = 0
-            n_ints = arr.size
-            dev = self.token_ids.device
-            if self._pinned is not None and self._pinned.numel() >= self._pinned_used + n_ints:
-                # the rest of the step's staging buffer: no copy has to wait for pageable memory
-                stage = self._pinned[self._pinned_used:self._pinned_used + n_ints]
-                self._pinned_used += n_ints
-                stage.numpy()[:] = arr.reshape(-1)
-                cached = torch.empty(n_ints, dtype=torch.int32, device=dev)
-                cached.copy_(stage, non_blocking=True)
-                cached = cached.view(-1, 4)
-                if self.after_staged_copy is not None:
-                    self.after_staged_copy()
-            else:
-                cached = torch.from_numpy(arr).to(dev)
+            cached = self._to_device(arr.reshape(-1)).view(-1, 4)
             self._tiles[tile_tokens] = cached
+        return cached
+
+    def _to_device(self, arr: np.ndarray) -> torch.Tensor:
+        """A small int32 list of this step on the device, through the rest of the step's staging buffer when there
+        is room (no copy then has to wait for pageable memory)."""
+        n_ints = arr.size
+        dev = self.token_ids.device
+        if self._pinned is not None and self._pinned.numel() >= self._pinned_used + n_ints:
+            stage = self._pinned[self._pinned_used:self._pinned_used + n_ints]
+            self._pinned_used += n_ints
+            stage.numpy()[:] = arr.reshape(-1)
+            out = torch.empty(n_ints, dtype=torch.int32, device=dev)
+            out.copy_(stage, non_blocking=True)
+            if self.after_staged_copy is not None:
+                self.after_staged_copy()
+            return out
+        return torch.from_numpy(np.ascontiguousarray(arr.reshape(-1), dtype=np.int32)).to(dev)
+
+    def scan_pieces(self, piece_tokens: int):
+        """Every request's tokens of this step cut into pieces of at most ``piece_tokens`` consecutive tokens, for a
+        recurrence that runs the pieces side by side: (int32 [n_pieces, 2] rows [first token row, the row past the
+        last), a request's pieces in a row; int32 [requests + 1], the first piece of every request).  Made once per
+        piece size."""
+        cached = self._tiles.get(("pieces", piece_tokens))
+        if cached is None:
+            pieces, first = [], [0]
+            start = 0
+            for n in self.seq_lens:
+                for t0 in range(0, n, piece_tokens):
+                    pieces.append((start + t0, start + min(t0 + piece_tokens, n)))
+                first.append(len(pieces))
+                start += n
+            both = self._to_device(np.concatenate([np.asarray(pieces, dtype=np.int32).reshape(-1), np.asarray(first, dtype=np.int32)]))
+            cached = (both[:2 * len(pieces)].view(-1, 2), both[2 * len(pieces):])
+            self._tiles[("pieces", piece_tokens)] = cached
         return cached
 
     @staticmethod
@@ -184,13 +221,4 @@ class StepBatch:
 
     def cache_view(self, owner: int, writable: bool = True) -> CacheView:
         """The cache of schedule entry ``owner`` as this batch's requests see it."""
-        cm = self.cache_manager
-        g = cm.group_of_layer.get(owner)
-        if g is not None:
-            grp = cm.groups[g]
-            return CacheView(k=grp.k[owner], v=grp.v[owner], block_table=self.block_tables[g], writable=writable,
-                             page_size=cm.page_size)
-        sg = cm.state_group_of_layer.get(owner)
-        if sg is not None:
-            return CacheView(state=cm.state_groups[sg].state[owner], writable=writable)
-        return CacheView(writable=False)
+        return cache_view_of(self.cache_manager, owner, self.block_tables, writable)

@@ -19,7 +19,7 @@ import numpy as np
 import torch
 
 from .. import ops
-from .batch import CacheView, StepBatch
+from .batch import CacheView, StepBatch, cache_view_of
 from .runtime import AHEAD_MAX_BATCH
 
 
@@ -101,16 +101,7 @@ class DecodeBatch:
         self._seen = [None] * self.n_seqs
 
     def cache_view(self, owner: int, writable: bool = True) -> CacheView:
-        cm = self.cache_manager
-        g = cm.group_of_layer.get(owner)
-        if g is not None:
-            grp = cm.groups[g]
-            return CacheView(k=grp.k[owner], v=grp.v[owner], block_table=self.block_tables[g], writable=writable,
-                             page_size=cm.page_size)
-        sg = cm.state_group_of_layer.get(owner)
-        if sg is not None:
-            return CacheView(state=cm.state_groups[sg].state[owner], writable=writable)
-        return CacheView(writable=False)
+        return cache_view_of(self.cache_manager, owner, self.block_tables, writable)
 
 
 class DecodeGraph:

@@ -51,6 +51,9 @@ class Runtime:
         self.result = torch.zeros(MAX_RESULT + 1, dtype=torch.int32, device=self.device)
         self.status = self.result[MAX_RESULT:]
         self.gemm_backend = gemm
+        # the type of a product that is a delta for the residual stream (``partials_ok``) when it comes as one tensor;
+        # None: the compute type.  A model whose sums into the stream read float32 deltas only sets float32.
+        self.delta_dtype: Optional[torch.dtype] = None
         self.attention_backend = "auto"
         # Asking L2 for weights ahead of their reader: only inside a captured decode step of few
         # requests, which sets ``side`` (a stream beside the step's chain) for the capture.
@@ -64,7 +67,7 @@ class Runtime:
         """y = x . w^T (+ bias); x [M,K], w [N,K] in the compute type, y in ``out_dtype``.
         With ``partials_ok`` the caller accepts ``ops.Partials`` (the partial sums of a product
         cut along K, which the next kernel adds up) in place of a tensor."""
-        out_dtype = out_dtype or self.dtype
+        out_dtype = out_dtype or (self.delta_dtype if partials_ok and self.delta_dtype is not None else self.dtype)
         if self.dtype == torch.float32:
             out = torch.empty((x.shape[0], w.shape[0]), dtype=out_dtype, device=x.device)
             return ops.gemm_f32(x, w, out, bias)
@@ -140,15 +143,16 @@ class Runtime:
                                   window, self.status, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first)
 
     # ---- mixture of experts ------------------------------------------------------------
-    def moe_experts(self, h, ids, wts, w_gu, w_down) -> torch.Tensor:
+    def moe_experts(self, h, ids, wts, w_gu, w_down, gated: bool = True, also=None, also_w=None) -> torch.Tensor:
         """The chosen experts' weighted outputs, float32 [tokens, width]: a block per (token, expert) for few
         tokens and on the 32-bit path; for many, tiles of one expert's rows as grouped products on tcgen05
-        (``LGML_MOE_GROUPED=mma``: the same tiles on ``mma.sync``)."""
-        if ids.numel() >= MOE_GROUPED_ROWS and ops.moe_grouped_supports(h, w_gu):
-            if os.environ.get("LGML_MOE_GROUPED") == "mma":
+        (``LGML_MOE_GROUPED=mma``: the same tiles on ``mma.sync``).  ``gated`` False: experts without a gate and
+        relu squared; ``also`` / ``also_w``: a term every token gets beside its experts' and its weight on it."""
+        if ids.numel() >= MOE_GROUPED_ROWS and ops.moe_grouped_supports(h, w_gu, gated):
+            if os.environ.get("LGML_MOE_GROUPED") == "mma" and gated and also is None:
                 return ops.moe_experts_grouped(h, ids, wts, w_gu, w_down)
-            return ops.moe_experts_tcgen05(h, ids, wts, w_gu, w_down, self.status)
-        return ops.moe_experts_rows(h, ids, wts, w_gu, w_down)
+            return ops.moe_experts_tcgen05(h, ids, wts, w_gu, w_down, self.status, gated=gated, also=also, also_w=also_w)
+        return ops.moe_experts_rows(h, ids, wts, w_gu, w_down, gated=gated, also=also, also_w=also_w)
 
     # ---- faults ------------------------------------------------------------------------
     def check_status(self, code: Optional[int] = None) -> None:

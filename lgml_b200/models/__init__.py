@@ -4,6 +4,7 @@ from .decoder import DecoderModel, LayerCall
 from . import llama  # noqa: F401  (registers LlamaForCausalLM)
 from . import lefulorn  # noqa: F401  (registers Lefulorn)
 from . import gotulorn  # noqa: F401  (registers Gotulorn)
+from . import konovik  # noqa: F401  (registers Konovik)
 
 
 def build_model(config):

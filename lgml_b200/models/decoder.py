@@ -26,14 +26,18 @@ from ..weights import TensorSpec
 class LayerCall:
     block: int                    # index into DecoderModel.blocks
     cache: Optional[int] = None   # index of the call that owns the cache used; None = this call
+    add_input: bool = False       # the residual stream as it was before the first call is added to it before this call
 
 
 class DecoderModel:
     def __init__(self, config, embedding, blocks, final_norm, head, schedule: Optional[List[LayerCall]] = None,
                  block_prefix: str = "model.layers.{}", final_norm_prefix: str = "model.norm",
                  embed_scale: Optional[float] = None, logit_scale: Optional[float] = None, logit_softcap: Optional[float] = None,
-                 ignored_tensors: Sequence[str] = (), embed_norm=None, embed_norm_prefix: str = "model.embed_norm"):
+                 ignored_tensors: Sequence[str] = (), embed_norm=None, embed_norm_prefix: str = "model.embed_norm",
+                 delta_dtype: Optional[torch.dtype] = None):
         self.config = config
+        # the type in which mixers and feed-forwards hand their results to the residual stream (None: the compute type)
+        self.delta_dtype = delta_dtype
         self.embedding = embedding
         self.blocks = list(blocks)
         self.final_norm = final_norm
@@ -104,8 +108,15 @@ class DecoderModel:
             ops.scale_cap(x, self.embed_scale)
         if self.embed_norm is not None:
             x = self.embed_norm.forward(rt, x, torch.float32)
+        rt.delta_dtype = self.delta_dtype
+        x_in = x.clone() if any(call.add_input for call in self.schedule) else None
         pending = None
         for ci, call in enumerate(self.schedule):
+            if call.add_input:
+                if pending is not None:
+                    ops.residual_fold(x, pending)
+                    pending = None
+                ops.residual_fold(x, x_in)
             owner = ci if call.cache is None else call.cache
             cache = batch.cache_view(owner, writable=call.cache is None)
             x, pending = self.blocks[call.block].forward(rt, x, pending, batch, cache)

@@ -202,8 +202,8 @@ class Partials:
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, delta=None,
-            rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out = rmsnorm(x [+ delta]) * weight.  With ``delta`` (a tensor, or ``Partials``) and
+            rows: Optional[torch.Tensor] = None, delta_scale: float = 1.0) -> torch.Tensor:
+    """out = rmsnorm(x [+ delta_scale * delta]) * weight.  With ``delta`` (a tensor, or ``Partials``) and
     no ``rows`` the sum is written back to x (the residual add); with ``rows`` output row r
     reads x[rows[r]]."""
     _need(x, "norm input", torch.float32, 2)
@@ -231,10 +231,10 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
         if delta.shape != x.shape or not delta.is_contiguous():
             raise KernelError("rmsnorm: delta must have the input's shape and be contiguous")
         ddt, dptr = dtype_code(delta.dtype), delta
-    fn = _fn("elementwise", "lgml_rmsnorm", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                             c_int, c_int, c_float, c_void_p])
+    fn = _fn("elementwise", "lgml_rmsnorm_scaled", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                    c_int, c_int, c_float, c_float, c_void_p])
     _check("elementwise", fn(_ptr(x), _ptr(dptr), ddt, n_parts, stride, _ptr(dbias), _ptr(weight), _ptr(rows), _ptr(out),
-                             dtype_code(out.dtype), n_rows, width, float(eps), _stream()), "rmsnorm")
+                             dtype_code(out.dtype), n_rows, width, float(eps), float(delta_scale), _stream()), "rmsnorm")
     return out
 
 
@@ -754,7 +754,7 @@ def diff_combine(maps: torch.Tensor, out: torch.Tensor, n_heads: int, n_key_head
 
 def latent_prepare(q_proj: torch.Tensor, down: torch.Tensor, norm_w: torch.Tensor, eps: float, inv_freq: torch.Tensor, n_rot: int,
                    positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, cells: torch.Tensor, n_heads: int,
-                   head_dim: int, rot_dim: int, rank: int, status: torch.Tensor, write_kv: bool = True):
+                   head_dim: int, rot_dim: int, rank: int, status: torch.Tensor, write_kv: bool = True, rot_mag: float = 1.0):
     """Latent attention between its projections and attention.  ``q_proj`` float32 [tokens, H (D + Dr)]
     (per head D plain, then Dr rotated entries), ``down`` float32 [tokens, R + Dr].  The first R columns
     of ``down``, over their root mean square, times ``norm_w``, are the latent c; the last Dr are a key
@@ -762,7 +762,8 @@ def latent_prepare(q_proj: torch.Tensor, down: torch.Tensor, norm_w: torch.Tenso
     the float32 frequencies and what float32 lost of them).  [c | rotated part] goes into the token's
     cell of ``cells`` [pages, 1, page, R + Dr].  Returns (q_plain [tokens, H D], q_full [tokens,
     H (R + Dr)]) in the cells' type; of q_full only the rotated Dr entries behind each head's first R
-    are written (``head_linear`` fills those)."""
+    are written (``head_linear`` fills those).  ``rot_mag`` multiplies every cosine and sine (a frequency
+    scaling that lengthens the rotated vectors)."""
     _need(q_proj, "query projection", torch.float32, 2)
     _need(down, "down projection", torch.float32, 2)
     _need(cells, "latent cells", ndim=4)
@@ -786,17 +787,19 @@ def latent_prepare(q_proj: torch.Tensor, down: torch.Tensor, norm_w: torch.Tenso
     q_full = torch.empty((n, n_heads * (rank + rot_dim)), dtype=cells.dtype, device=cells.device)
     fn = _fn("attention_heads", "lgml_latent_prepare", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_void_p,
                                                         c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
-                                                        c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+                                                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p])
     _check("attention_heads", fn(_ptr(q_proj), ldq, _ptr(down), ldd, _ptr(norm_w), float(eps), _ptr(inv_freq[0]), _ptr(inv_freq[1]), int(n_rot),
                                  _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(cells), dtype_code(cells.dtype),
                                  n_pages, page, _ptr(q_plain), q_plain.stride(0), _ptr(q_full), q_full.stride(0), n, n_heads, head_dim, rot_dim,
-                                 rank, 1 if write_kv else 0, _ptr(status), _stream()), "latent_prepare")
+                                 rank, 1 if write_kv else 0, float(rot_mag), _ptr(status), _stream()), "latent_prepare")
     return q_plain, q_full
 
 
-def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head_stride: int, out_head_stride: int) -> torch.Tensor:
+def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head_stride: int, out_head_stride: int,
+                gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """A product per head: out[t, h * out_head_stride + o] = sum_k x[t, h * x_head_stride + k] w[h, o, k];
-    ``w`` [H, O, K] contiguous, x and out 2-D with dense rows, all of one type (float32 sums)."""
+    ``w`` [H, O, K] contiguous, x and out 2-D with dense rows, all of one type (float32 sums).  With ``gate``
+    (float32, the output's columns, dense rows) the result is multiplied by sigmoid(gate)."""
     _need(x, "head_linear input", ndim=2)
     _need(w, "head_linear weights", x.dtype, 3)
     _need(out, "head_linear output", x.dtype, 2)
@@ -805,9 +808,16 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head_stri
     n = x.shape[0]
     if not w.is_contiguous() or out.shape[0] != n or (H - 1) * x_head_stride + K > x.shape[1] or (H - 1) * out_head_stride + O > out.shape[1]:
         raise KernelError(f"head_linear: x {tuple(x.shape)} / w {tuple(w.shape)} / out {tuple(out.shape)} with head strides {x_head_stride}, {out_head_stride} do not fit")
-    fn = _fn("attention_heads", "lgml_head_linear", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    ldg = 0
+    if gate is not None:
+        _need(gate, "head_linear gate", torch.float32, 2)
+        ldg = _rows_contiguous(gate, "head_linear gate")
+        if gate.shape[0] != n or (H - 1) * out_head_stride + O > gate.shape[1]:
+            raise KernelError(f"head_linear: gate {tuple(gate.shape)} does not cover the output's columns")
+    fn = _fn("attention_heads", "lgml_head_linear", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                                     c_int, c_void_p])
     _check("attention_heads", fn(_ptr(x), ldx, int(x_head_stride), _ptr(w), _ptr(out), ldo, int(out_head_stride), dtype_code(x.dtype), n, H, O, K,
-                                 _stream()), "head_linear")
+                                 _ptr(gate), ldg, _stream()), "head_linear")
     return out
 
 
@@ -815,14 +825,24 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head_stri
 # mixture of experts
 # ----------------------------------------------------------------------------------------
 
-def moe_router(h: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor], top: int):
+ROUTER_MODES = {"softmax": 0, "sigmoid": 1}
+
+
+def moe_router(h: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor], top: int, mode: str = "softmax",
+               route_scale: float = 1.0, n_extra: int = 0):
     """The ``top`` experts with the largest float32 logits W_r h + b_r per token (ties: the lower index)
-    and the softmax over those logits alone: (ids int32 [tokens, top], weights float32 [tokens, top])."""
+    and the softmax over those logits alone: (ids int32 [tokens, top], weights float32 [tokens, top]).
+    ``mode`` "sigmoid": the scores are sigmoid(W_r h); the experts with the largest score + b_r are chosen, and
+    the weights are the chosen scores over their sum (+ 1e-20), times ``route_scale``.  ``n_extra``: the last
+    rows of ``w_router`` are no experts; the sigmoids of their logits come back as a third result
+    float32 [tokens, n_extra]."""
     _need(h, "router input", ndim=2)
     _need(w_router, "router weight", torch.float32, 2)
     ldh = _rows_contiguous(h, "router input")
     n, E = h.shape
-    X = w_router.shape[0]
+    X = w_router.shape[0] - int(n_extra)
+    if mode not in ROUTER_MODES or n_extra < 0 or X <= 0:
+        raise KernelError(f"moe_router: mode '{mode}' with {n_extra} extra rows of {w_router.shape[0]}")
     if w_router.shape[1] != E or not w_router.is_contiguous() or not 0 < top <= X:
         raise KernelError(f"moe_router: weight {tuple(w_router.shape)} does not fit rows of {E}, or {top} of {X} experts")
     if b_router is not None:
@@ -831,12 +851,25 @@ def moe_router(h: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch
             raise KernelError("moe_router: one bias per expert")
     ids = torch.empty((n, top), dtype=torch.int32, device=h.device)
     wts = torch.empty((n, top), dtype=torch.float32, device=h.device)
-    fn = _fn("moe", "lgml_moe_router", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
-    _check("moe", fn(_ptr(h), dtype_code(h.dtype), ldh, _ptr(w_router), _ptr(b_router), _ptr(ids), _ptr(wts), n, E, X, int(top), _stream()), "moe_router")
-    return ids, wts
+    extra = torch.empty((n, n_extra), dtype=torch.float32, device=h.device) if n_extra else None
+    fn = _fn("moe", "lgml_moe_router_mode", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
+                                             c_int, c_void_p, c_void_p])
+    _check("moe", fn(_ptr(h), dtype_code(h.dtype), ldh, _ptr(w_router), _ptr(b_router), _ptr(ids), _ptr(wts), n, E, X, int(top), ROUTER_MODES[mode],
+                     float(route_scale), int(n_extra), _ptr(extra), _stream()), "moe_router")
+    return (ids, wts, extra) if n_extra else (ids, wts)
 
 
-def _moe_shapes(h, ids, wts, w_gu, w_down, who: str):
+def _also(also, also_w, n: int, E: int, who: str):
+    """A term every token gets beside its experts' (float32 [tokens, E]) and the token's weight on it (float32 [tokens])."""
+    if also is None:
+        return
+    _need(also, "shared term", torch.float32, 2)
+    _need(also_w, "shared term's weights", torch.float32)
+    if tuple(also.shape) != (n, E) or also_w.numel() != n or not also.is_contiguous() or not also_w.is_contiguous():
+        raise KernelError(f"{who}: shared term {tuple(also.shape)} with weights {tuple(also_w.shape)} does not fit [{n}, {E}]")
+
+
+def _moe_shapes(h, ids, wts, w_gu, w_down, who: str, gated: bool = True):
     for t, what in ((w_gu, "gate|up"), (w_down, "down")):
         _need(t, f"experts' {what} matrices", h.dtype, 3)
         if not t.is_contiguous():
@@ -845,37 +878,40 @@ def _moe_shapes(h, ids, wts, w_gu, w_down, who: str):
     _need(wts, "experts' weights", torch.float32, 2)
     n, E = h.shape
     X, F2, _ = w_gu.shape
-    F, top = F2 // 2, ids.shape[1]
-    if tuple(w_gu.shape) != (X, 2 * F, E) or tuple(w_down.shape) != (X, E, F) or tuple(ids.shape) != (n, top) \
+    F, top = (F2 // 2 if gated else F2), ids.shape[1]
+    if tuple(w_gu.shape) != (X, 2 * F if gated else F, E) or tuple(w_down.shape) != (X, E, F) or tuple(ids.shape) != (n, top) \
             or tuple(wts.shape) != (n, top) or not ids.is_contiguous() or not wts.is_contiguous():
         raise KernelError(f"{who}: shapes disagree: h {tuple(h.shape)}, gate|up {tuple(w_gu.shape)}, down {tuple(w_down.shape)}, ids {tuple(ids.shape)}")
     return n, E, F, X, top
 
 
-def moe_experts_rows(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+def moe_experts_rows(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, gated: bool = True,
+                     also: Optional[torch.Tensor] = None, also_w: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t] = sum_s wts[t, s] W_down[e] (silu(W_gate[e] h_t) * (W_up[e] h_t)), e = ids[t, s]: float32
     [tokens, E].  The experts' matrices stacked: ``w_gu`` [X, 2 F, E] with the gate row of a feature followed
     by its up row, ``w_down`` [X, E, F].  A block per (token, chosen expert): the form for few tokens and for
-    the 32-bit path."""
+    the 32-bit path.  ``gated`` False: experts without a gate, ``w_gu`` [X, F, E] and the activation relu squared.
+    ``also`` / ``also_w``: out += also_w[t] * also[t] (a shared expert's output and the token's gate on it)."""
     _need(h, "experts' input", ndim=2)
     ldh = _rows_contiguous(h, "experts' input")
-    n, E, F, X, top = _moe_shapes(h, ids, wts, w_gu, w_down, "moe_experts_rows")
+    n, E, F, X, top = _moe_shapes(h, ids, wts, w_gu, w_down, "moe_experts_rows", gated)
+    _also(also, also_w, n, E, "moe_experts_rows")
     act = torch.empty((n * top, F), dtype=h.dtype, device=h.device)
     out = torch.empty((n, E), dtype=torch.float32, device=h.device)
-    fn = _fn("moe", "lgml_moe_experts_rows", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                              c_int, c_int, c_int, c_void_p])
+    fn = _fn("moe", "lgml_moe_experts_rows_form", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                   c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
     _check("moe", fn(_ptr(h), dtype_code(h.dtype), ldh, _ptr(ids), _ptr(wts), _ptr(w_gu), _ptr(w_down), _ptr(act), _ptr(out), n, E, F, X,
-                     top, _stream()), "moe_experts_rows")
+                     top, 0 if gated else 1, _ptr(also), _ptr(also_w), _stream()), "moe_experts_rows")
     return out
 
 
 MOE_TILE_ROWS = 128
 
 
-def moe_grouped_supports(h: torch.Tensor, w_gu: torch.Tensor) -> bool:
+def moe_grouped_supports(h: torch.Tensor, w_gu: torch.Tensor, gated: bool = True) -> bool:
     """Whether the grouped forms take these operands: bfloat16, widths that are multiples of 8."""
     return (h.dtype == torch.bfloat16 and h.dim() == 2 and h.stride(1) == 1 and h.stride(0) % 8 == 0 and h.data_ptr() % 16 == 0
-            and w_gu.shape[1] % 16 == 0 and w_gu.shape[2] % 8 == 0)
+            and w_gu.shape[1] % (16 if gated else 8) == 0 and w_gu.shape[2] % 8 == 0)
 
 
 def _moe_tiles(n_rows: int, X: int) -> int:
@@ -907,16 +943,19 @@ def moe_experts_grouped(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w
 
 
 def moe_experts_tcgen05(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor,
-                        status: torch.Tensor) -> torch.Tensor:
+                        status: torch.Tensor, gated: bool = True, also: Optional[torch.Tensor] = None,
+                        also_w: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``moe_experts_rows`` for many tokens, bfloat16, on tcgen05: the (token, chosen expert) rows are sorted by
     expert on the device, the tokens' rows gathered into tiles of 128 rows of one expert, and the two products
     run as grouped products of the tcgen05 kernel (a tile reads the matrices of its expert; the gate|up product
     applies the SiLU gate in its epilogue); a token's rows are then added, weighted, in the order of its experts.
-    float32 [tokens, E].  No host value is read."""
+    float32 [tokens, E].  No host value is read.  ``gated`` False: experts without a gate (``w_gu`` [X, F, E], the
+    first product's epilogue is relu squared); ``also`` / ``also_w`` as for ``moe_experts_rows``."""
     _need(h, "experts' input", torch.bfloat16, 2)
     ldh = _rows_contiguous(h, "experts' input")
-    n, E, F, X, top = _moe_shapes(h, ids, wts, w_gu, w_down, "moe_experts_tcgen05")
-    if not moe_grouped_supports(h, w_gu):
+    n, E, F, X, top = _moe_shapes(h, ids, wts, w_gu, w_down, "moe_experts_tcgen05", gated)
+    _also(also, also_w, n, E, "moe_experts_tcgen05")
+    if not moe_grouped_supports(h, w_gu, gated):
         raise KernelError("moe_experts_tcgen05: widths and row strides must be multiples of 8 and the input 16-byte aligned")
     n_rows = n * top
     max_tiles = _moe_tiles(n_rows, X)
@@ -935,13 +974,163 @@ def moe_experts_tcgen05(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w
     _check("moe", fn(_ptr(h), ldh, _ptr(rows), _ptr(tiles), max_tiles, _ptr(a_perm), _ptr(pos), E, top, stream), "moe_gather_rows")
     fn = _fn("gemm_tcgen05", "lgml_gemm_tcgen05_grouped", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                                            c_void_p, c_void_p])
-    _check("gemm_tcgen05", fn(_ptr(a_perm), _ptr(w_gu), _ptr(act), 0, max_tiles, 2 * F, E, X, F, _ptr(tiles), 1, _ptr(status), stream),
-           "gemm_tcgen05_grouped")
+    _check("gemm_tcgen05", fn(_ptr(a_perm), _ptr(w_gu), _ptr(act), 0, max_tiles, 2 * F if gated else F, E, X, F, _ptr(tiles), 1 if gated else 2,
+                              _ptr(status), stream), "gemm_tcgen05_grouped")
     _check("gemm_tcgen05", fn(_ptr(act), _ptr(w_down), _ptr(y), 1, max_tiles, E, F, X, E, _ptr(tiles), 0, _ptr(status), stream),
            "gemm_tcgen05_grouped")
-    fn = _fn("moe", "lgml_moe_weighted_sum", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check("moe", fn(_ptr(y), _ptr(pos), _ptr(wts), _ptr(out), n, E, top, stream), "moe_weighted_sum")
+    fn = _fn("moe", "lgml_moe_weighted_sum_also", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check("moe", fn(_ptr(y), _ptr(pos), _ptr(wts), _ptr(out), n, E, top, _ptr(also), _ptr(also_w), stream), "moe_weighted_sum")
     return out
+
+
+# ----------------------------------------------------------------------------------------
+# token shift, the minGRU recurrence, the per-layer token input
+# ----------------------------------------------------------------------------------------
+
+def _delta_parts(delta, x: torch.Tensor, who: str):
+    """(pointer tensor, parts, stride between parts, bias) of a float32 delta or ``Partials`` for x's rows."""
+    if delta is None:
+        return None, 1, 0, None
+    if isinstance(delta, Partials):
+        d = delta.data
+        _need(d, "residual delta parts", torch.float32, 3)
+        if tuple(d.shape[1:]) != tuple(x.shape) or not d.is_contiguous():
+            raise KernelError(f"{who}: delta parts must be [parts, rows, width] and contiguous")
+        return d, d.shape[0], d.shape[1] * d.shape[2], delta.bias
+    _need(delta, "residual delta", torch.float32, 2)
+    if delta.shape != x.shape or not delta.is_contiguous():
+        raise KernelError(f"{who}: delta must be float32 of the input's shape and contiguous")
+    return delta, 1, 0, None
+
+
+def _state_rows(state: torch.Tensor, width: int, who: str) -> int:
+    _need(state, "state slots", torch.float32, 2)
+    if state.stride(1) != 1 or state.shape[1] < width:
+        raise KernelError(f"{who}: the state's rows must be dense and hold {width} floats, not {tuple(state.shape)}")
+    return state.stride(0)
+
+
+def token_shift(h: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, seq_of_token: torch.Tensor, seq_start: torch.Tensor,
+                slots: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = h[t] + (h[t - 1] - h[t]) * mu per channel, within each request; the row before a request's first
+    token of this step is ``state[slot]`` (zeros for a new request), which then takes the step's last row of h.
+    h float32 [tokens, W]; ``state`` float32 [slots, >= W] (rows may be part of wider rows)."""
+    _need(h, "token shift input", torch.float32, 2)
+    _need(mu, "token shift weights", torch.float32, 1)
+    _need(out, "token shift output", ndim=2)
+    n, W = h.shape
+    if not h.is_contiguous() or not out.is_contiguous() or tuple(out.shape) != (n, W) or mu.numel() != W:
+        raise KernelError(f"token_shift: shapes disagree: h {tuple(h.shape)}, mu {tuple(mu.shape)}, out {tuple(out.shape)}")
+    ld = _state_rows(state, W, "token_shift")
+    fn = _fn("token_mix", "lgml_token_shift", [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check("token_mix", fn(_ptr(h), _ptr(mu), _ptr(state), ld, _ptr(seq_of_token), _ptr(seq_start), _ptr(slots), _ptr(out), dtype_code(out.dtype), n, W,
+                           _stream()), "token_shift")
+    return out
+
+
+def mingru_chunk_tokens() -> int:
+    fn = getattr(csrc.load("token_mix"), "lgml_mingru_chunk_tokens")
+    fn.argtypes, fn.restype = [], c_int
+    return fn()
+
+
+def mingru_scan(proj: torch.Tensor, state: torch.Tensor, seq_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor,
+                chunks: Optional[torch.Tensor] = None, chunk_start: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The minGRU recurrence over every request's tokens of this step: ``proj`` float32 [tokens, 3 W] holds per token
+    the gate's logits a, the candidate's input u and the output gate's input g; z = sigmoid(a), c = u + 1/2 (u >= 0) or
+    sigmoid(u); S <- (1 - z) S + z c from ``state[slot]`` (which takes the last S); out[t] = S_t * silu(g_t).
+    With ``chunks`` (int32 [n, 2], token rows [first, past the last) of pieces of the requests' portions, a request's
+    pieces in a row) and ``chunk_start`` (int32 [requests + 1]) the pieces run side by side: their products of
+    (1 - z) and scans from zero first, a chain over a request's pieces, then every piece from its true start."""
+    _need(proj, "minGRU projections", torch.float32, 2)
+    _need(out, "minGRU output", ndim=2)
+    n = proj.shape[0]
+    W = out.shape[1]
+    ld = _rows_contiguous(proj, "minGRU projections")
+    if proj.shape[1] != 3 * W or out.shape[0] != n or not out.is_contiguous():
+        raise KernelError(f"mingru_scan: projections {tuple(proj.shape)} do not fit an output of {tuple(out.shape)}")
+    sld = _state_rows(state, W, "mingru_scan")
+    n_seqs = slots.numel()
+    if chunks is None:
+        fn = _fn("token_mix", "lgml_mingru_scan", [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+        _check("token_mix", fn(_ptr(proj), ld, _ptr(state), sld, _ptr(seq_start), _ptr(slots), _ptr(out), dtype_code(out.dtype), n_seqs, W, _stream()),
+               "mingru_scan")
+        return out
+    _need(chunks, "chunks", torch.int32, 2)
+    _need(chunk_start, "chunk starts", torch.int32, 1)
+    n_chunks = chunks.shape[0]
+    if chunks.shape[1] != 2 or not chunks.is_contiguous() or chunk_start.numel() != n_seqs + 1:
+        raise KernelError("mingru_scan: chunks are [n, 2] and chunk starts one more than the requests")
+    ab = torch.empty((2, n_chunks, W), dtype=torch.float32, device=proj.device)
+    fn = _fn("token_mix", "lgml_mingru_chunks", [c_void_p, c_int, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_int, c_int, c_void_p])
+    _check("token_mix", fn(_ptr(proj), ld, _ptr(state), sld, _ptr(chunks), _ptr(chunk_start), n_chunks, _ptr(slots), _ptr(ab), _ptr(out),
+                           dtype_code(out.dtype), n_seqs, W, _stream()), "mingru_chunks")
+    return out
+
+
+def residual_fold(x: torch.Tensor, delta, scale: float = 1.0, copy_dtype: Optional[torch.dtype] = None):
+    """x += scale * delta (a float32 tensor or ``Partials``; None: nothing is added), and, with ``copy_dtype``, x in
+    that type as a second result."""
+    _need(x, "residual stream", torch.float32, 2)
+    if not x.is_contiguous():
+        raise KernelError("residual_fold: the residual stream must be contiguous")
+    dptr, n_parts, stride, dbias = _delta_parts(delta, x, "residual_fold")
+    xb = torch.empty(x.shape, dtype=copy_dtype, device=x.device) if copy_dtype is not None else None
+    fn = _fn("token_mix", "lgml_side_fold", [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check("token_mix", fn(_ptr(x), _ptr(dptr), n_parts, stride, _ptr(dbias), float(scale), _ptr(xb), dtype_code(copy_dtype) if xb is not None else F32,
+                           x.shape[0], x.shape[1], _stream()), "residual_fold")
+    return xb
+
+
+def token_side(x: torch.Tensor, delta, delta_scale: float, token_ids: torch.Tensor, table: torch.Tensor, col0: int, w_gate: torch.Tensor,
+               w_proj: torch.Tensor, norm_w: torch.Tensor, eps: float, out_scale: float) -> torch.Tensor:
+    """In place on the float32 residual stream, one kernel: x += delta_scale * delta; y = W_proj (gelu_tanh(W_gate x) *
+    table[token, col0 : col0 + dim]); x += out_scale * y / rms(y) * norm_w."""
+    _need(x, "residual stream", torch.float32, 2)
+    _need(table, "token table", w_gate.dtype, 2)
+    _need(w_gate, "side gate", ndim=2)
+    _need(w_proj, "side projection", w_gate.dtype, 2)
+    _need(norm_w, "side norm weight", torch.float32, 1)
+    _need(token_ids, "token ids", torch.int32, 1)
+    n, W = x.shape
+    dim = w_gate.shape[0]
+    if not x.is_contiguous() or tuple(w_gate.shape) != (dim, W) or tuple(w_proj.shape) != (W, dim) or norm_w.numel() != W or token_ids.numel() != n \
+            or not w_gate.is_contiguous() or not w_proj.is_contiguous() or table.stride(1) != 1:
+        raise KernelError(f"token_side: shapes disagree: x {tuple(x.shape)}, gate {tuple(w_gate.shape)}, proj {tuple(w_proj.shape)}")
+    dptr, n_parts, stride, dbias = _delta_parts(delta, x, "token_side")
+    fn = _fn("token_mix", "lgml_token_side", [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                              c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int, c_int, c_void_p])
+    _check("token_mix", fn(_ptr(x), _ptr(dptr), n_parts, stride, _ptr(dbias), float(delta_scale), _ptr(token_ids), _ptr(table), table.stride(0), int(col0),
+                           table.shape[0], _ptr(w_gate), _ptr(w_proj), _ptr(norm_w), float(eps), float(out_scale), dtype_code(w_gate.dtype), n, W, dim,
+                           _stream()), "token_side")
+    return x
+
+
+def side_gate(gate: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, col0: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """g[t, j] = gelu_tanh(gate[t, j]) * table[token_t, col0 + j]; gate float32 [tokens, dim], g in the table's type."""
+    _need(gate, "side gate logits", torch.float32, 2)
+    _need(table, "token table", out_dtype, 2)
+    n, dim = gate.shape
+    if not gate.is_contiguous() or table.stride(1) != 1 or token_ids.numel() != n:
+        raise KernelError("side_gate: shapes disagree")
+    g = torch.empty((n, dim), dtype=out_dtype, device=gate.device)
+    fn = _fn("token_mix", "lgml_side_gate", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check("token_mix", fn(_ptr(gate), _ptr(token_ids), _ptr(table), table.stride(0), int(col0), table.shape[0], _ptr(g), dtype_code(out_dtype), n, dim,
+                           _stream()), "side_gate")
+    return g
+
+
+def side_add(x: torch.Tensor, y: torch.Tensor, norm_w: torch.Tensor, eps: float, out_scale: float) -> torch.Tensor:
+    """x += out_scale * y / rms(y) * norm_w, row by row; both float32."""
+    _need(x, "residual stream", torch.float32, 2)
+    _need(y, "side output", torch.float32, 2)
+    _need(norm_w, "side norm weight", torch.float32, 1)
+    if x.shape != y.shape or not x.is_contiguous() or not y.is_contiguous() or norm_w.numel() != x.shape[1]:
+        raise KernelError("side_add: shapes disagree")
+    fn = _fn("token_mix", "lgml_side_add", [c_void_p, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p])
+    _check("token_mix", fn(_ptr(x), _ptr(y), _ptr(norm_w), float(eps), float(out_scale), x.shape[0], x.shape[1], _stream()), "side_add")
+    return x
 
 
 # ----------------------------------------------------------------------------------------

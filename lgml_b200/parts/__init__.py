@@ -5,6 +5,8 @@ from .embedding import LMHead, TokenEmbedding
 from .delta import ChannelDelta
 from .diff_attention import DifferentialAttention
 from .latent_attention import LatentAttention
+from .mingru import MinGRU
+from .token_mix import TokenShift, TokenSide
 from .moe import RoutedExperts
 from .mlp import ClampedGLU, DenseMLP, GatedMLP
 from .norm import DynamicTanh, RMSNorm
@@ -12,4 +14,4 @@ from .sink_attention import SinkAttention
 from .rope import NoPosition, Rope, RotaryPosition, frequency_factors, store_kv
 
 __all__ = ["Attention", "KINDS", "Part", "make_part", "register_part", "registered", "PreNormBlock", "LMHead",
-           "TokenEmbedding", "GatedMLP", "DenseMLP", "ClampedGLU", "RoutedExperts", "ChannelDelta", "SinkAttention", "DifferentialAttention", "LatentAttention", "RMSNorm", "DynamicTanh", "NoPosition", "Rope", "RotaryPosition", "frequency_factors", "store_kv"]
+           "TokenEmbedding", "GatedMLP", "DenseMLP", "ClampedGLU", "RoutedExperts", "ChannelDelta", "SinkAttention", "DifferentialAttention", "LatentAttention", "MinGRU", "TokenShift", "TokenSide", "RMSNorm", "DynamicTanh", "NoPosition", "Rope", "RotaryPosition", "frequency_factors", "store_kv"]

@@ -24,6 +24,8 @@ Interfaces (tensors are torch tensors on the device; ``rt`` is the ``Runtime``):
 * mixer:        ``cache_spec() -> PagedKV | FixedState | None``,
                 ``forward(rt, h, batch, cache) -> delta``  (h, delta: [tokens, width])
 * feed-forward: ``forward(rt, h) -> delta``; optionally ``first_weights() -> [tensor]``
+* token input:  something a layer carries from token to token, or adds of the token itself, around its
+                mixer and feed-forward (``parts/token_mix.py``)
 * block:        ``forward(rt, x, pending, batch, cache) -> (x, pending)`` where
                 ``pending`` is a delta not yet added to the residual stream x
 """
@@ -33,7 +35,7 @@ from typing import Any, Callable, Dict, List
 
 from ..weights import TensorSpec
 
-KINDS = ("norm", "position", "mixer", "feed_forward", "block")
+KINDS = ("norm", "position", "mixer", "feed_forward", "token_input", "block")
 _PARTS: Dict[str, Dict[str, Callable[..., Any]]] = {k: {} for k in KINDS}
 
 

@@ -13,24 +13,28 @@ from .base import Part, register_part
 
 class GatedMLP(Part):
     graph_safe = True
-    def __init__(self, width: int, inner: int, activation: str = "silu", bias: bool = False):
+    def __init__(self, width: int, inner: int, activation: str = "silu", bias: bool = False,
+                 names=(".gate_proj.weight", ".up_proj.weight", ".down_proj.weight")):
         if activation != "silu":
             raise ValueError(f"activation '{activation}' is not supported (only 'silu')")
         self.width, self.inner, self.bias = width, inner, bool(bias)
+        self.names = tuple(names)       # what the three matrices' names add to the part's prefix: gate, up, down
+        if self.bias and self.names != (".gate_proj.weight", ".up_proj.weight", ".down_proj.weight"):
+            raise ValueError("biases come with the default tensor names only")
         self.wgu = self.bgu = self.wd = self.bd = None
 
     def tensor_specs(self, prefix):
         E, F = self.width, self.inner
-        specs = [TensorSpec(prefix + ".gate_proj.weight", (F, E)), TensorSpec(prefix + ".up_proj.weight", (F, E)),
-                 TensorSpec(prefix + ".down_proj.weight", (E, F))]
+        specs = [TensorSpec(prefix + self.names[0], (F, E)), TensorSpec(prefix + self.names[1], (F, E)),
+                 TensorSpec(prefix + self.names[2], (E, F))]
         if self.bias:
             specs += [TensorSpec(prefix + ".gate_proj.bias", (F,), VECTOR), TensorSpec(prefix + ".up_proj.bias", (F,), VECTOR),
                       TensorSpec(prefix + ".down_proj.bias", (E,), VECTOR)]
         return specs
 
     def bind(self, prefix, tensors, rt):
-        wg, wu = tensors[prefix + ".gate_proj.weight"], tensors[prefix + ".up_proj.weight"]
-        self.wd = tensors[prefix + ".down_proj.weight"]
+        wg, wu = tensors[prefix + self.names[0]], tensors[prefix + self.names[1]]
+        self.wd = tensors[prefix + self.names[2]]
         bg = bu = None
         if self.bias:
             bg, bu = tensors[prefix + ".gate_proj.bias"], tensors[prefix + ".up_proj.bias"]

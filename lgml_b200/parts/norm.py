@@ -11,25 +11,31 @@ from .base import Part, register_part
 
 
 class RMSNorm(Part):
+    """``single``: the learned weight is ONE number for all coordinates (a tensor without dimensions);
+    the kernel reads it as a row of equal entries."""
+
     graph_safe = True
-    def __init__(self, width: int, eps: float, suffix: str = ".weight"):
+    def __init__(self, width: int, eps: float, suffix: str = ".weight", single: bool = False):
         self.width = width
         self.eps = float(eps)
         self.suffix = suffix        # what the weight's name adds to the part's prefix ("" when the prefix is the name)
+        self.single = bool(single)
         self.weight = None
 
     def tensor_specs(self, prefix):
-        return [TensorSpec(prefix + self.suffix, (self.width,), VECTOR, init=(1.0, 1.0))]
+        return [TensorSpec(prefix + self.suffix, () if self.single else (self.width,), VECTOR, init=(1.0, 1.0))]
 
     def bind(self, prefix, tensors, rt):
         self.weight = tensors[prefix + self.suffix]
+        if self.single:
+            self.weight = self.weight.reshape(1).expand(self.width).contiguous()
 
-    def forward(self, rt, x, out_dtype, delta=None, rows=None):
-        """Norm of x (+ delta).  x is the float32 residual stream; with ``delta`` the sum
+    def forward(self, rt, x, out_dtype, delta=None, rows=None, delta_scale: float = 1.0):
+        """Norm of x (+ delta_scale * delta).  x is the float32 residual stream; with ``delta`` the sum
         is written back to x.  ``rows`` (int32 on the device) picks the rows to norm."""
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.width), dtype=out_dtype, device=x.device)
-        return ops.rmsnorm(x, self.weight, self.eps, out, delta=delta, rows=rows)
+        return ops.rmsnorm(x, self.weight, self.eps, out, delta=delta, rows=rows, delta_scale=delta_scale)
 
 
 class DynamicTanh(Part):
