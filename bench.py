@@ -16,7 +16,7 @@ measured copy bandwidth, and ``roofline_points`` the same fraction for every bat
 
 ``--shape llama32_3b`` runs that shape's own workload (32 prompts of 128 to 4,096 tokens in
 portions of 512 beside decodes, 512 new tokens each) through ``Engine.generate``;
-``--shape llama2_13b`` decodes at batch 16 after 3,584-token prompts; ``--design lefulorn`` (or ``gotulorn``)
+``--shape llama2_13b`` decodes at batch 16 after 3,584-token prompts; ``--design lefulorn`` (or ``gotulorn``, ``konovik``)
 times that design beside the Llama decoder at equal layer sizes; ``--cpu-baseline`` times the
 plain CPU implementation at the tiny configurations.
 """
@@ -319,7 +319,27 @@ def gotulorn_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int
     return {"architecture": "Gotulorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "layers": out}
 
 
-DESIGN_SHAPES = {"lefulorn": lefulorn_shape, "gotulorn": gotulorn_shape}
+def konovik_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, layers: int, window: int, vocab: int) -> dict:
+    """Konovik with layers of a real model's size: minGRU layers of the model's width with the gated feed-forward and
+    latent-attention layers in turn (a latent of 96 and a rotated part of 32, which is what the tensor-core attention
+    kernels take; a window; stretched frequencies; an output gate) with 8 experts of a quarter of the gated inner width,
+    2 of them chosen, and a shared expert of that size; a token input of 64 numbers per layer; no loop (the Llama
+    decoder beside it runs every layer once)."""
+    inner = (2 * ff // 3 + 255) // 256 * 256
+    out = []
+    for i in range(layers):
+        if i % 2 == 0:
+            out.append({"type": "mingru", "mixer": {"width": width}, "mlp": {"kind": "dense", "ff": inner}})
+        else:
+            m = {"heads": heads, "dim": head_dim // 2, "rot_dim": 32, "vdim": head_dim // 2, "kv_rank": 96, "scale": (head_dim // 2 + 32) ** -0.5,
+                 "mask": {"size": window}, "rot": {"base": 10000.0, "dims": 32, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+            out.append({"type": "latent_attention", "mixer": m,
+                        "mlp": {"kind": "moe", "expert": {"ff": inner // 4}, "router": {"experts": 8, "top": 2, "scale": 2.0}, "shared": {"ff": inner // 4}}})
+    return {"architecture": "Konovik", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "token_side": {"dim": 64},
+            "layers": out}
+
+
+DESIGN_SHAPES = {"lefulorn": lefulorn_shape, "gotulorn": gotulorn_shape, "konovik": konovik_shape}
 
 DESIGN_SIZES = {          # name -> width, heads, KV heads, head size, dense inner width, layers
     "w2048": (2048, 16, 4, 128, 8192, 4),
@@ -438,7 +458,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0, help="context (tokens a request may hold) instead of the shape's own")
     ap.add_argument("--prefill-tokens", type=int, default=0, help="tokens of the timed prompt instead of 2,048 (read in portions of 2,048)")
     ap.add_argument("--no-kernel-times", action="store_true", help="leave out the per-kernel-class times of a decode step")
-    ap.add_argument("--design", default="", choices=["", "lefulorn", "gotulorn"], help="time this design beside the Llama decoder at equal layer sizes "
+    ap.add_argument("--design", default="", choices=["", "lefulorn", "gotulorn", "konovik"], help="time this design beside the Llama decoder at equal layer sizes "
                     "(prefill and decode, with kernel-class times) instead of the headline workload")
     ap.add_argument("--cpu-baseline", action="store_true", help="time the plain CPU implementation at the tiny configurations and stop")
     args = ap.parse_args()

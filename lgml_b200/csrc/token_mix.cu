@@ -192,20 +192,53 @@ __global__ void __launch_bounds__(128) mingru_chunk_scan_kernel(const float *__r
 
 __device__ __forceinline__ float gelu_tanh(float z) { return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
 
+// Sixteen bytes of a weight row as floats: 8 of bfloat16, 4 of float32.
+template <typename T> struct RowVec;
+template <> struct RowVec<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float *p, float (&v)[4]) {
+        const float4 r = __ldg(reinterpret_cast<const float4 *>(p));
+        v[0] = r.x, v[1] = r.y, v[2] = r.z, v[3] = r.w;
+    }
+};
+template <> struct RowVec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16 *p, float (&v)[8]) {
+        const uint4 r = __ldg(reinterpret_cast<const uint4 *>(p));
+        const unsigned w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v[2 * i] = __uint_as_float(w[i] << 16), v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+};
+
+// acc + the dot product of N weights with N floats of shared memory that start on a 16-byte border
+template <int N> __device__ __forceinline__ float dot_shared(const float *s, const float (&w)[N], float acc) {
+#pragma unroll
+    for (int i = 0; i < N; i += 4) {
+        const float4 v = *reinterpret_cast<const float4 *>(s + i);
+        acc = fmaf(v.x, w[i], fmaf(v.y, w[i + 1], fmaf(v.z, w[i + 2], fmaf(v.w, w[i + 3], acc))));
+    }
+    return acc;
+}
+
 // One block per token.  x float32 [n, W] in place; delta float32 [parts, n, W] or null (its parts added in
 // order, then its bias, the sum times delta_scale into x); table [vocab, ld_table] whose columns
 // col0 .. col0 + dim - 1 are this layer's; wg [dim, W], wp [W, dim] in T; norm_w float32 [W].
-template <typename T>
-__global__ void __launch_bounds__(256) token_side_kernel(float *__restrict__ x, const float *__restrict__ delta, int n_parts, long long part_stride,
+// WIDE: W and dim are multiples of 16 bytes of T and both matrices start on such a border.  Then a warp
+// reads a row of wg sixteen bytes a lane, two rows at a time, and `lanes` lanes (a power of two) share a row of wp,
+// so that every load of a warp covers whole lines.  Otherwise element by element.
+template <typename T, bool WIDE>
+__global__ void __launch_bounds__(512) token_side_kernel(float *__restrict__ x, const float *__restrict__ delta, int n_parts, long long part_stride,
                                                          const float *__restrict__ delta_bias, float delta_scale, const int *__restrict__ token_ids,
                                                          const T *__restrict__ table, int ld_table, int col0, int vocab, const T *__restrict__ wg,
                                                          const T *__restrict__ wp, const float *__restrict__ norm_w, float eps, float out_scale,
-                                                         int W, int dim) {
+                                                         int W, int dim, int lanes) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ __align__(16) float sm[];         // x row [W], y [W], g [dim]
     __shared__ float red[32];
     float *xs = sm, *ys = sm + W, *gs = sm + 2 * W;
+    constexpr int V = RowVec<T>::N;
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     float *xr = x + (size_t)t * W;
@@ -222,21 +255,77 @@ __global__ void __launch_bounds__(256) token_side_kernel(float *__restrict__ x, 
     __syncthreads();
     int id = token_ids[t];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);           // the embedding kernel has flagged such an id
-    for (int j = warp; j < dim; j += n_warps) {
-        const T *w = wg + (size_t)j * W;
-        float dot = 0.f;
-        for (int k = lane; k < W; k += 32) dot = fmaf(xs[k], to_f32(w[k]), dot);
-        dot = warp_sum(dot);
-        if (lane == 0) gs[j] = gelu_tanh(dot) * to_f32(table[(size_t)id * ld_table + col0 + j]);
+    const T *e = table + (size_t)id * ld_table + col0;
+    if (WIDE) {
+        for (int j = 2 * warp; j < dim; j += 2 * n_warps) {
+            const bool two = j + 1 < dim;
+            const T *w0 = wg + (size_t)j * W, *w1 = w0 + (two ? W : 0);
+            float d0 = 0.f, d1 = 0.f;
+#pragma unroll 4
+            for (int k = lane * V; k < W; k += 32 * V) {
+                float a[V], b[V];
+                RowVec<T>::load(w0 + k, a);
+                RowVec<T>::load(w1 + k, b);
+                d0 = dot_shared<V>(xs + k, a, d0), d1 = dot_shared<V>(xs + k, b, d1);
+            }
+            d0 = warp_sum(d0), d1 = warp_sum(d1);
+            if (lane == 0) {
+                gs[j] = gelu_tanh(d0) * to_f32(e[j]);
+                if (two) gs[j + 1] = gelu_tanh(d1) * to_f32(e[j + 1]);
+            }
+        }
+    } else {
+        for (int j = warp; j < dim; j += n_warps) {
+            const T *w = wg + (size_t)j * W;
+            float dot = 0.f;
+            for (int k = lane; k < W; k += 32) dot = fmaf(xs[k], to_f32(w[k]), dot);
+            dot = warp_sum(dot);
+            if (lane == 0) gs[j] = gelu_tanh(dot) * to_f32(e[j]);
+        }
     }
     __syncthreads();
     float ss = 0.f;
-    for (int k = threadIdx.x; k < W; k += blockDim.x) {
-        const T *w = wp + (size_t)k * dim;
-        float y = 0.f;
-        for (int j = 0; j < dim; ++j) y = fmaf(gs[j], to_f32(w[j]), y);
-        ys[k] = y;
-        ss = fmaf(y, y, ss);
+    if (WIDE) {
+        // U row groups a warp at a time, their loads all in flight before the first product
+        constexpr int U = 4;
+        const int rows = 32 / lanes, sub = lane % lanes;         // rows of wp that one load of a warp covers
+        const bool mine = sub * V < dim;
+        for (int k0 = warp * rows * U; k0 < W; k0 += n_warps * rows * U) {
+            float a[U][V], y[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int k = k0 + u * rows + lane / lanes;
+                if (k < W && mine) RowVec<T>::load(wp + (size_t)k * dim + sub * V, a[u]);
+                else {
+#pragma unroll
+                    for (int i = 0; i < V; ++i) a[u][i] = 0.f;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int k = k0 + u * rows + lane / lanes;
+                y[u] = mine ? dot_shared<V>(gs + sub * V, a[u], 0.f) : 0.f;
+                if (k < W)
+                    for (int c = (sub + lanes) * V; c < dim; c += lanes * V) {      // rows longer than 32 lanes hold at once
+                        float b[V];
+                        RowVec<T>::load(wp + (size_t)k * dim + c, b);
+                        y[u] = dot_shared<V>(gs + c, b, y[u]);
+                    }
+                for (int o = lanes >> 1; o > 0; o >>= 1) y[u] += __shfl_xor_sync(0xffffffffu, y[u], o);
+                if (sub == 0 && k < W) {
+                    ys[k] = y[u];
+                    ss = fmaf(y[u], y[u], ss);
+                }
+            }
+        }
+    } else {
+        for (int k = threadIdx.x; k < W; k += blockDim.x) {
+            const T *w = wp + (size_t)k * dim;
+            float y = 0.f;
+            for (int j = 0; j < dim; ++j) y = fmaf(gs[j], to_f32(w[j]), y);
+            ys[k] = y;
+            ss = fmaf(y, y, ss);
+        }
     }
     ss = block_sum(ss, red);
     const float inv = out_scale / sqrtf(ss / (float)W + eps);
@@ -361,10 +450,15 @@ LGML_API int lgml_token_side(float *x, const float *delta, int n_parts, long lon
     LGML_REQUIRE(smem <= 200 * 1024, "token_side: rows of %d and %d entries do not fit shared memory", W, dim);
 #define LGML_SIDE(T)                                                                                                                         \
     do {                                                                                                                                     \
-        if (smem > 48 * 1024 && cudaFuncSetAttribute(token_side_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+        constexpr int V = RowVec<T>::N;                                                                                                      \
+        const bool wide = W % V == 0 && dim % V == 0 && ((uintptr_t)wg | (uintptr_t)wp) % 16 == 0;                                           \
+        int lanes = 1;                                                                                                                       \
+        while (lanes < 32 && lanes * V < dim) lanes *= 2;                                                                                    \
+        auto kernel = wide ? token_side_kernel<T, true> : token_side_kernel<T, false>;                                                       \
+        if (smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)          \
             LGML_FAIL("token_side: cannot have %zu bytes of shared memory", smem);                                                           \
-        lgml_launch(token_side_kernel<T>, n_tokens, 256, smem, stream, x, delta, n_parts, part_stride, delta_bias, delta_scale, token_ids,    \
-                    (const T *)table, ld_table, col0, vocab, (const T *)wg, (const T *)wp, norm_w, eps, out_scale, W, dim);                   \
+        lgml_launch(kernel, n_tokens, 512, smem, stream, x, delta, n_parts, part_stride, delta_bias, delta_scale, token_ids,                  \
+                    (const T *)table, ld_table, col0, vocab, (const T *)wg, (const T *)wp, norm_w, eps, out_scale, W, dim, lanes);            \
     } while (0)
     if (dtype == LGML_F32) LGML_SIDE(float);
     else if (dtype == LGML_BF16) LGML_SIDE(__nv_bfloat16);

@@ -12,7 +12,7 @@ float32 rows (the norm before it writes them so) and gives rows in the compute t
     e = table[token, col0 : col0 + dim];   y = W_proj (gelu_tanh(W_gate x) * e);   x += m y / rms(y) * w
 
 x is the residual stream itself (not a norm of it).  For a few tokens one kernel does all of it
-(and the residual sum before it); for many, the two products run as matrix products.
+(and the residual sum before it); for many, in bfloat16, the two products run as matrix products.
 """
 from __future__ import annotations
 
@@ -70,7 +70,7 @@ class TokenSide(Part):
     def forward(self, rt, x, pending, scale, batch):
         """x += scale * pending, then x += scale * (the token input's normed output); all in place."""
         n = x.shape[0]
-        if n < SIDE_PRODUCTS_FROM:
+        if n < SIDE_PRODUCTS_FROM or rt.dtype == torch.float32:      # float32: one order of summation whatever the step holds
             return ops.token_side(x, pending, scale, batch.token_ids, self.table, self.col0, self.w_gate, self.w_proj, self.norm_w, self.eps, scale)
         xb = ops.residual_fold(x, pending, scale, copy_dtype=rt.dtype if rt.dtype != torch.float32 else None)
         gate = rt.linear(x if xb is None else xb, self.w_gate, out_dtype=torch.float32)

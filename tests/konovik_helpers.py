@@ -141,7 +141,7 @@ def random_weights(cfg: dict, seed: int, sharpen: float = 1.0) -> Dict[str, torc
                     w[p + "mlp.shared.up"], w[p + "mlp.shared.down"], w[p + "mlp.shared.sg"] = mat(Fs, E, 2.0), mat(E, Fs), mat(1, E, 2.0)
         if side:
             n = side["dim"]
-            w[p + "side.gate"], w[p + "side.proj"], w[p + "side.norm"] = mat(n, E, 2.0), mat(E, n), vec(E, 0.2, 1.0)
+            w[p + "side.gate"], w[p + "side.proj"], w[p + "side.norm"] = mat(n, E, 0.5), mat(E, n), vec(E, 0.2, 1.0)
     return {n: t.to(torch.bfloat16).float() for n, t in w.items()}
 
 
@@ -177,21 +177,26 @@ def oracle_logits(cfg: dict, weights: Dict[str, torch.Tensor], ids: List[int]) -
     return _oracle[key]
 
 
-def clear_ids(cfg: dict, weights: Dict[str, torch.Tensor], n: int, seed: int, gap: float = 0.02) -> List[int]:
-    """n random token ids for which no router of the plain model decides by less than ``gap`` (the choice
-    scores are sigmoids plus a correction, so they lie close together): a bfloat16 run may not rest on a close
-    call between two experts.  The model is causal, so the first close call is redrawn and the sequence
-    checked again."""
+def clear_ids(cfg: dict, weights: Dict[str, torch.Tensor], n: int, seed: int, gap: float = 0.02, small: float = 0.2) -> List[int]:
+    """n random token ids on which a bfloat16 run may be compared: no router of the plain model decides by less
+    than ``gap`` (the choice scores are sigmoids plus a correction, so they lie close together), and no token
+    input is smaller than ``small`` times that layer's median before it is divided by its root mean square (a
+    few numbers per layer can all but cancel, and the unit vector made of the rest magnifies every rounding
+    ahead of it).  The model is causal, so the first such position is redrawn and the sequence checked again."""
     import random
 
     rng = random.Random(seed)
     ids = [rng.randrange(cfg["vocab"]) for _ in range(n)]
     for _ in range(40 * n):
         gaps: list = []
-        P.forward(cfg, numpy_of(weights), ids, router_gaps=gaps)
-        if not gaps:
-            return ids
-        close = np.nonzero(np.min(np.stack(gaps), axis=0) < gap)[0]
+        sizes: list = []
+        P.forward(cfg, numpy_of(weights), ids, router_gaps=gaps, side_sizes=sizes)
+        bad = np.zeros(n, dtype=bool)
+        if gaps:
+            bad |= np.min(np.stack(gaps), axis=0) < gap
+        for r in sizes:
+            bad |= r < small * max(float(np.median(r)), 1e-3)
+        close = np.nonzero(bad)[0]
         if close.size == 0:
             return ids
         ids[int(close[0])] = rng.randrange(cfg["vocab"])

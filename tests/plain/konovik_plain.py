@@ -157,10 +157,13 @@ def routed_ff(h, W, p, f, gaps=None):
     return out
 
 
-def side_input(x, W, p, e, eps):
+def side_input(x, W, p, e, eps, sizes=None):
     """What a layer adds from its own small token table: y = W_proj (gelu_tanh(W_gate x) e), then y
-    over its root mean square times a plain weight."""
+    over its root mean square times a plain weight.  ``sizes``, a list, receives the root mean square of y
+    per token: where it is tiny, the result is a unit vector of whatever the last bits of y hold."""
     y = (gelu_tanh(x @ W[p + ".gate"].T) * e) @ W[p + ".proj"].T
+    if sizes is not None:
+        sizes.append(np.sqrt(np.mean(y * y, axis=-1)))
     return rms_unit(y, eps) * W[p + ".norm"]
 
 
@@ -178,9 +181,9 @@ def layer_runs(cfg):
     return runs + [(i, False) for i in range(b, n)]
 
 
-def forward(cfg, W, tokens, return_layers=False, router_gaps=None):
+def forward(cfg, W, tokens, return_layers=False, router_gaps=None, side_sizes=None):
     """Logits [T, vocab] of a whole sequence (and, on request, the residual stream after every layer
-    run; ``router_gaps``, a list, receives one array per routed layer run)."""
+    run; ``router_gaps``, a list, receives one array per routed layer run, ``side_sizes`` one per token input)."""
     eps, m = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
     ids = np.asarray(tokens)
     x0 = scalar_norm(W["embed"][ids], W["embed.norm"], eps)
@@ -207,7 +210,7 @@ def forward(cfg, W, tokens, return_layers=False, router_gaps=None):
             x = x + m * (dense_ff(h, W, p + ".mlp") if f["kind"] == "dense" else routed_ff(h, W, p + ".mlp", f, router_gaps))
         if side:
             n = side["dim"]
-            x = x + m * side_input(x, W, p + ".side", W["side.embed"][ids, i * n:(i + 1) * n], eps)
+            x = x + m * side_input(x, W, p + ".side", W["side.embed"][ids, i * n:(i + 1) * n], eps, side_sizes)
         layers.append(x.copy())
     logits = scalar_norm(x, W["final.norm"], eps) @ W["head"].T
     return (logits, layers) if return_layers else logits
