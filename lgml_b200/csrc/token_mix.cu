@@ -12,6 +12,7 @@
 //
 // Everything here is float32 arithmetic in both compute types; only the results that feed a
 // matrix product (token_shift's y, the scan's out) are stored in the compute type.
+#include <cooperative_groups.h>
 #include <math.h>
 
 #include "common.cuh"
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(128) mingru_scan_kernel(const float *__restric
 //   pass 1: per (chunk, channel): A = prod (1 - z), B = the scan's end from S = 0
 //   pass 2: per (request, channel): S at the start of every chunk (written over B), and the slot's new state
 //   pass 3: per (chunk, channel): the scan from its start, out = S silu(g)
-constexpr int CHUNK = 64;
+constexpr int CHUNK = 32;
 __global__ void __launch_bounds__(128) mingru_chunk_ends_kernel(const float *__restrict__ proj, int ld, const int *__restrict__ chunks,
                                                                 float *__restrict__ A, float *__restrict__ B, int W) {
     pdl_trigger();
@@ -155,10 +156,18 @@ __global__ void __launch_bounds__(128) mingru_chain_kernel(const float *__restri
     if (c >= W) return;
     float *st = state + (size_t)slots[s] * state_ld + c;
     float S = act_load(st);
-    for (int k = chunk_start[s]; k < chunk_start[s + 1]; ++k) {
-        const float a = act_load(A + (size_t)k * W + c), b = act_load(B + (size_t)k * W + c);
-        B[(size_t)k * W + c] = S;                   // the state this chunk starts from
-        S = fmaf(a, S, b);
+    const int k1 = chunk_start[s + 1];
+    for (int k = chunk_start[s]; k < k1; k += 8) {          // eight chunks' pairs in flight, then the chain through them
+        float a[8], b[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (k + i < k1) a[i] = act_load(A + (size_t)(k + i) * W + c), b[i] = act_load(B + (size_t)(k + i) * W + c);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (k + i < k1) {
+                B[(size_t)(k + i) * W + c] = S;             // the state this chunk starts from
+                S = fmaf(a[i], S, b[i]);
+            }
     }
     *st = S;
 }
@@ -221,26 +230,33 @@ template <int N> __device__ __forceinline__ float dot_shared(const float *s, con
     return acc;
 }
 
-// One block per token.  x float32 [n, W] in place; delta float32 [parts, n, W] or null (its parts added in
-// order, then its bias, the sum times delta_scale into x); table [vocab, ld_table] whose columns
-// col0 .. col0 + dim - 1 are this layer's; wg [dim, W], wp [W, dim] in T; norm_w float32 [W].
+// A cluster of `cs` blocks per token (cs = 1: a block, no cluster).  x float32 [n, W] in place; delta float32
+// [parts, n, W] or null (its parts added in order, then its bias, the sum times delta_scale into x); table
+// [vocab, ld_table] whose columns col0 .. col0 + dim - 1 are this layer's; wg [dim, W], wp [W, dim] in T; norm_w float32 [W].
+// Every block holds the whole row of x.  The gates are dealt out over the blocks of the cluster and read back from
+// their shared memory; block r then owns rows r * ceil(W / cs) .. of wp, of y and of x, and the sum of squares
+// is added up over the cluster in the order of the ranks.  With few tokens in a step this is what puts the two
+// matrices' bytes on many SMs instead of one per token.
 // WIDE: W and dim are multiples of 16 bytes of T and both matrices start on such a border.  Then a warp
 // reads a row of wg sixteen bytes a lane, two rows at a time, and `lanes` lanes (a power of two) share a row of wp,
 // so that every load of a warp covers whole lines.  Otherwise element by element.
-template <typename T, bool WIDE>
+template <typename T, bool WIDE, bool CLUSTERED>
 __global__ void __launch_bounds__(512) token_side_kernel(float *__restrict__ x, const float *__restrict__ delta, int n_parts, long long part_stride,
                                                          const float *__restrict__ delta_bias, float delta_scale, const int *__restrict__ token_ids,
                                                          const T *__restrict__ table, int ld_table, int col0, int vocab, const T *__restrict__ wg,
                                                          const T *__restrict__ wp, const float *__restrict__ norm_w, float eps, float out_scale,
-                                                         int W, int dim, int lanes) {
+                                                         int W, int dim, int lanes, int cs) {
+    namespace cg = cooperative_groups;
     pdl_trigger();
     pdl_wait();
-    extern __shared__ __align__(16) float sm[];         // x row [W], y [W], g [dim]
+    extern __shared__ __align__(16) float sm[];         // x row [W], y [W], g [dim], this block's gates [dim]
     __shared__ float red[32];
-    float *xs = sm, *ys = sm + W, *gs = sm + 2 * W;
+    __shared__ float slice_ss;
+    float *xs = sm, *ys = sm + W, *gs = sm + 2 * W, *mine_g = gs + dim;
     constexpr int V = RowVec<T>::N;
-    const int t = blockIdx.x;
+    const int t = CLUSTERED ? blockIdx.x / cs : blockIdx.x, rank = CLUSTERED ? blockIdx.x % cs : 0;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int per = (W + cs - 1) / cs, lo = min(W, rank * per), hi = min(W, lo + per);       // this block's rows
     float *xr = x + (size_t)t * W;
     for (int k = threadIdx.x; k < W; k += blockDim.x) {
         float v = act_load(xr + k);
@@ -256,8 +272,9 @@ __global__ void __launch_bounds__(512) token_side_kernel(float *__restrict__ x, 
     int id = token_ids[t];
     id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);           // the embedding kernel has flagged such an id
     const T *e = table + (size_t)id * ld_table + col0;
+    float *g_out = CLUSTERED ? mine_g : gs;
     if (WIDE) {
-        for (int j = 2 * warp; j < dim; j += 2 * n_warps) {
+        for (int j = 2 * (rank * n_warps + warp); j < dim; j += 2 * n_warps * cs) {
             const bool two = j + 1 < dim;
             const T *w0 = wg + (size_t)j * W, *w1 = w0 + (two ? W : 0);
             float d0 = 0.f, d1 = 0.f;
@@ -270,17 +287,25 @@ __global__ void __launch_bounds__(512) token_side_kernel(float *__restrict__ x, 
             }
             d0 = warp_sum(d0), d1 = warp_sum(d1);
             if (lane == 0) {
-                gs[j] = gelu_tanh(d0) * to_f32(e[j]);
-                if (two) gs[j + 1] = gelu_tanh(d1) * to_f32(e[j + 1]);
+                g_out[j] = gelu_tanh(d0) * to_f32(e[j]);
+                if (two) g_out[j + 1] = gelu_tanh(d1) * to_f32(e[j + 1]);
             }
         }
     } else {
-        for (int j = warp; j < dim; j += n_warps) {
+        for (int j = rank * n_warps + warp; j < dim; j += n_warps * cs) {
             const T *w = wg + (size_t)j * W;
             float dot = 0.f;
             for (int k = lane; k < W; k += 32) dot = fmaf(xs[k], to_f32(w[k]), dot);
             dot = warp_sum(dot);
-            if (lane == 0) gs[j] = gelu_tanh(dot) * to_f32(e[j]);
+            if (lane == 0) g_out[j] = gelu_tanh(dot) * to_f32(e[j]);
+        }
+    }
+    if (CLUSTERED) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        for (int j = threadIdx.x; j < dim; j += blockDim.x) {
+            const int owner = WIDE ? ((j >> 1) / n_warps) % cs : (j / n_warps) % cs;
+            gs[j] = *cluster.map_shared_rank(mine_g + j, owner);
         }
     }
     __syncthreads();
@@ -290,12 +315,12 @@ __global__ void __launch_bounds__(512) token_side_kernel(float *__restrict__ x, 
         constexpr int U = 4;
         const int rows = 32 / lanes, sub = lane % lanes;         // rows of wp that one load of a warp covers
         const bool mine = sub * V < dim;
-        for (int k0 = warp * rows * U; k0 < W; k0 += n_warps * rows * U) {
+        for (int k0 = lo + warp * rows * U; k0 < hi; k0 += n_warps * rows * U) {
             float a[U][V], y[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int k = k0 + u * rows + lane / lanes;
-                if (k < W && mine) RowVec<T>::load(wp + (size_t)k * dim + sub * V, a[u]);
+                if (k < hi && mine) RowVec<T>::load(wp + (size_t)k * dim + sub * V, a[u]);
                 else {
 #pragma unroll
                     for (int i = 0; i < V; ++i) a[u][i] = 0.f;
@@ -305,21 +330,21 @@ __global__ void __launch_bounds__(512) token_side_kernel(float *__restrict__ x, 
             for (int u = 0; u < U; ++u) {
                 const int k = k0 + u * rows + lane / lanes;
                 y[u] = mine ? dot_shared<V>(gs + sub * V, a[u], 0.f) : 0.f;
-                if (k < W)
+                if (k < hi)
                     for (int c = (sub + lanes) * V; c < dim; c += lanes * V) {      // rows longer than 32 lanes hold at once
                         float b[V];
                         RowVec<T>::load(wp + (size_t)k * dim + c, b);
                         y[u] = dot_shared<V>(gs + c, b, y[u]);
                     }
                 for (int o = lanes >> 1; o > 0; o >>= 1) y[u] += __shfl_xor_sync(0xffffffffu, y[u], o);
-                if (sub == 0 && k < W) {
+                if (sub == 0 && k < hi) {
                     ys[k] = y[u];
                     ss = fmaf(y[u], y[u], ss);
                 }
             }
         }
     } else {
-        for (int k = threadIdx.x; k < W; k += blockDim.x) {
+        for (int k = lo + threadIdx.x; k < hi; k += blockDim.x) {
             const T *w = wp + (size_t)k * dim;
             float y = 0.f;
             for (int j = 0; j < dim; ++j) y = fmaf(gs[j], to_f32(w[j]), y);
@@ -328,8 +353,16 @@ __global__ void __launch_bounds__(512) token_side_kernel(float *__restrict__ x, 
         }
     }
     ss = block_sum(ss, red);
+    if (CLUSTERED) {
+        cg::cluster_group cluster = cg::this_cluster();
+        if (threadIdx.x == 0) slice_ss = ss;
+        cluster.sync();
+        ss = 0.f;
+        for (int k = 0; k < cs; ++k) ss += *cluster.map_shared_rank(&slice_ss, k);
+    }
     const float inv = out_scale / sqrtf(ss / (float)W + eps);
-    for (int k = threadIdx.x; k < W; k += blockDim.x) xr[k] = fmaf(ys[k] * inv, __ldg(norm_w + k), xs[k]);
+    for (int k = lo + threadIdx.x; k < hi; k += blockDim.x) xr[k] = fmaf(ys[k] * inv, __ldg(norm_w + k), xs[k]);
+    if (CLUSTERED) cg::this_cluster().sync();     // no block leaves while another may still read its gates or its sum
 }
 
 // The pieces of the same for many tokens, where the two small products run as the framework's matrix products:
@@ -446,24 +479,35 @@ LGML_API int lgml_token_side(float *x, const float *delta, int n_parts, long lon
     LGML_REQUIRE(n_tokens >= 0 && W > 0 && dim > 0 && vocab > 0 && col0 >= 0 && col0 + dim <= ld_table, "token_side: bad sizes");
     LGML_REQUIRE(delta == nullptr || n_parts >= 1, "token_side: a delta has at least one part");
     if (n_tokens == 0) return 0;
-    const size_t smem = sizeof(float) * (2 * (size_t)W + dim);
+    const size_t smem = sizeof(float) * (2 * (size_t)W + 2 * (size_t)dim);
     LGML_REQUIRE(smem <= 200 * 1024, "token_side: rows of %d and %d entries do not fit shared memory", W, dim);
+    // blocks per token: as many as bring a step of few tokens onto most SMs (a cluster of up to 8)
+    // (float32 keeps one block: the order in which the squares are summed must not depend on what else is in the step)
+    const int cs = dtype == LGML_F32 ? 1 : n_tokens <= 18 ? 8 : n_tokens <= 37 ? 4 : n_tokens <= 74 ? 2 : 1;
+#define LGML_SIDE_FORM(T, WIDE, CL)                                                                                                          \
+    do {                                                                                                                                     \
+        auto kernel = token_side_kernel<T, WIDE, CL>;                                                                                        \
+        if (smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)          \
+            LGML_FAIL("token_side: cannot have %zu bytes of shared memory", smem);                                                           \
+        lgml_launch_cluster(kernel, n_tokens * cs, 512, smem, stream, cs, x, delta, n_parts, part_stride, delta_bias, delta_scale, token_ids, \
+                            (const T *)table, ld_table, col0, vocab, (const T *)wg, (const T *)wp, norm_w, eps, out_scale, W, dim, lanes, cs); \
+    } while (0)
 #define LGML_SIDE(T)                                                                                                                         \
     do {                                                                                                                                     \
         constexpr int V = RowVec<T>::N;                                                                                                      \
         const bool wide = W % V == 0 && dim % V == 0 && ((uintptr_t)wg | (uintptr_t)wp) % 16 == 0;                                           \
         int lanes = 1;                                                                                                                       \
         while (lanes < 32 && lanes * V < dim) lanes *= 2;                                                                                    \
-        auto kernel = wide ? token_side_kernel<T, true> : token_side_kernel<T, false>;                                                       \
-        if (smem > 48 * 1024 && cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)          \
-            LGML_FAIL("token_side: cannot have %zu bytes of shared memory", smem);                                                           \
-        lgml_launch(kernel, n_tokens, 512, smem, stream, x, delta, n_parts, part_stride, delta_bias, delta_scale, token_ids,                  \
-                    (const T *)table, ld_table, col0, vocab, (const T *)wg, (const T *)wp, norm_w, eps, out_scale, W, dim, lanes);            \
+        if (wide && cs > 1) LGML_SIDE_FORM(T, true, true);                                                                                   \
+        else if (wide) LGML_SIDE_FORM(T, true, false);                                                                                       \
+        else if (cs > 1) LGML_SIDE_FORM(T, false, true);                                                                                     \
+        else LGML_SIDE_FORM(T, false, false);                                                                                                \
     } while (0)
     if (dtype == LGML_F32) LGML_SIDE(float);
     else if (dtype == LGML_BF16) LGML_SIDE(__nv_bfloat16);
     else LGML_FAIL("token_side: unknown type %d", dtype);
 #undef LGML_SIDE
+#undef LGML_SIDE_FORM
     return lgml_launch_status("token_side");
 }
 

@@ -4,6 +4,9 @@
     python -m lgml_b200.kernel_bench decode_attention --batch 8 --context 2176 --heads 32 --kv-heads 8 --head-dim 128
     python -m lgml_b200.kernel_bench prefill_attention --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128
     python -m lgml_b200.kernel_bench rmsnorm --rows 8 --width 4096 --parts 9
+    python -m lgml_b200.kernel_bench token_shift --rows 2048 --width 4096
+    python -m lgml_b200.kernel_bench mingru --rows 2048 --width 4096 [--requests 8]
+    python -m lgml_b200.kernel_bench token_side --rows 8 --width 4096 --dim 64
 
 Each case is run over a ring of input buffers larger than the L2 cache, so that weights and
 cache pages come from HBM as they do in a decode step; warm-up launches first, then the timed
@@ -141,6 +144,81 @@ def case_rmsnorm(a) -> None:
     print(f"rmsnorm rows={rows} width={width} parts={parts} bf16_delta={a.bf16_delta}: {us:.2f} us, {byts / us / 1e3:.0f} GB/s")
 
 
+def case_token_shift(a) -> None:
+    rows, width, reqs = a.rows, a.width, a.requests
+    nb = min(ring(rows * width * 4), 16)
+    hs = [torch.randn(rows, width, device=DEV) for _ in range(nb)]
+    mu = torch.rand(width, device=DEV)
+    out = torch.empty(rows, width, dtype=torch.bfloat16, device=DEV)
+    state = torch.zeros(reqs, width, device=DEV)
+    per = rows // reqs
+    seq_start = torch.arange(0, reqs * per + 1, per, dtype=torch.int32, device=DEV)
+    seq_of = torch.arange(reqs, dtype=torch.int32, device=DEV).repeat_interleave(per).contiguous()
+    slots = torch.arange(reqs, dtype=torch.int32, device=DEV)
+    n = reqs * per
+    us = timed(lambda i: ops.token_shift(hs[i][:n], mu, state, seq_of, seq_start, slots, out[:n]), nb, a.warmup, a.iters)
+    byts = n * width * (4 + 2)
+    print(f"token_shift rows={n} width={width} requests={reqs}: {us:.2f} us, {byts / us / 1e3:.0f} GB/s")
+
+
+def case_mingru(a) -> None:
+    """The recurrence alone (the projections are a product of the framework's): sequential per channel for
+    short portions, in pieces side by side beyond ``MINGRU_PIECES_FROM`` tokens."""
+    rows, width, reqs = a.rows, a.width, a.requests
+    per = rows // reqs
+    n = reqs * per
+    nb = min(ring(n * 3 * width * 4), 8)
+    projs = [torch.randn(n, 3 * width, device=DEV) for _ in range(nb)]
+    out = torch.empty(n, width, dtype=torch.bfloat16, device=DEV)
+    state = torch.zeros(reqs, width, device=DEV)
+    seq_start = torch.arange(0, n + 1, per, dtype=torch.int32, device=DEV)
+    slots = torch.arange(reqs, dtype=torch.int32, device=DEV)
+    chunks = chunk_start = None
+    passes = 3
+    from .parts.mingru import MINGRU_PIECES_FROM
+
+    if per > MINGRU_PIECES_FROM:
+        c = ops.mingru_chunk_tokens()
+        pieces, first = [], [0]
+        for r in range(reqs):
+            pieces += [(r * per + t0, r * per + min(t0 + c, per)) for t0 in range(0, per, c)]
+            first.append(len(pieces))
+        chunks = torch.tensor(pieces, dtype=torch.int32, device=DEV)
+        chunk_start = torch.tensor(first, dtype=torch.int32, device=DEV)
+        passes = 5                           # z and u in the first pass, z, u and g in the last
+    us = timed(lambda i: ops.mingru_scan(projs[i], state, seq_start, slots, out, chunks, chunk_start), nb, a.warmup, a.iters)
+    byts = n * width * (4 * passes + 2)
+    print(f"mingru rows={n} width={width} requests={reqs} pieces={'yes' if chunks is not None else 'no'}: {us:.2f} us, {byts / us / 1e3:.0f} GB/s")
+
+
+def case_token_side(a) -> None:
+    """The token input: for few rows the one kernel (its traffic is the two small matrices, read once per
+    launch when they come from HBM); for many, the three small kernels around the two products."""
+    rows, width, dim, vocab = a.rows, a.width, a.dim, 32000
+    nb = max(min(ring(2 * dim * width * 2), 64), 2)
+    gates = [(torch.randn(dim, width, device=DEV) * 0.02).to(torch.bfloat16) for _ in range(nb)]
+    projs = [(torch.randn(width, dim, device=DEV) * 0.02).to(torch.bfloat16) for _ in range(nb)]
+    table = torch.randn(vocab, dim, device=DEV).to(torch.bfloat16)
+    ids = torch.randint(0, vocab, (rows,), dtype=torch.int32, device=DEV)
+    norm_w = torch.ones(width, device=DEV)
+    nx = min(ring(rows * width * 4), 16)
+    xs = [torch.randn(rows, width, device=DEV) for _ in range(nx)]
+    deltas = [torch.randn(rows, width, device=DEV) for _ in range(nx)]
+    if rows < 64:
+        us = timed(lambda i: ops.token_side(xs[i % nx], deltas[i % nx], 0.5, ids, table, 0, gates[i], projs[i], norm_w, 1e-6, 0.5), nb, a.warmup, a.iters)
+        byts = 2 * dim * width * 2 + rows * width * 12
+        print(f"token_side rows={rows} width={width} dim={dim}: {us:.2f} us, {byts / us / 1e3:.0f} GB/s")
+        return
+    ys = [torch.randn(rows, width, device=DEV) for _ in range(nx)]
+    gl = [torch.randn(rows, dim, device=DEV) for _ in range(nx)]
+    us = timed(lambda i: ops.residual_fold(xs[i], deltas[i], 0.5, copy_dtype=torch.bfloat16), nx, a.warmup, a.iters)
+    print(f"side_fold rows={rows} width={width}: {us:.2f} us, {rows * width * 14 / us / 1e3:.0f} GB/s")
+    us = timed(lambda i: ops.side_gate(gl[i], ids, table, 0, torch.bfloat16), nx, a.warmup, a.iters)
+    print(f"side_gate rows={rows} dim={dim}: {us:.2f} us, {rows * dim * 8 / us / 1e3:.0f} GB/s")
+    us = timed(lambda i: ops.side_add(xs[i], ys[i], norm_w, 1e-6, 0.5), nx, a.warmup, a.iters)
+    print(f"side_add rows={rows} width={width}: {us:.2f} us, {rows * width * 12 / us / 1e3:.0f} GB/s")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m lgml_b200.kernel_bench")
     ap.add_argument("--warmup", type=int, default=5)
@@ -175,13 +253,20 @@ def main(argv=None) -> int:
     r.add_argument("--width", type=int, default=4096)
     r.add_argument("--parts", type=int, default=9)
     r.add_argument("--bf16-delta", action="store_true", help="add a bfloat16 delta (a product's output) instead of float32 partial sums")
+    for name in ("token_shift", "mingru", "token_side"):
+        t = sub.add_parser(name)
+        t.add_argument("--rows", type=int, default=2048)
+        t.add_argument("--width", type=int, default=4096)
+        t.add_argument("--requests", type=int, default=1)
+        t.add_argument("--dim", type=int, default=64)
     a = ap.parse_args(argv)
     global USE_GRAPH
     USE_GRAPH = not a.no_graph
     if not torch.cuda.is_available():
         print("kernel_bench needs a CUDA device", file=sys.stderr)
         return 1
-    {"gemm": case_gemm, "decode_attention": case_decode_attention, "prefill_attention": case_prefill_attention, "rmsnorm": case_rmsnorm}[a.case](a)
+    {"gemm": case_gemm, "decode_attention": case_decode_attention, "prefill_attention": case_prefill_attention, "rmsnorm": case_rmsnorm,
+     "token_shift": case_token_shift, "mingru": case_mingru, "token_side": case_token_side}[a.case](a)
     return 0
 
 

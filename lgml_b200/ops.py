@@ -128,7 +128,9 @@ class _Timed:
 _wrapped = {}
 
 
-def _fn(lib_name: str, fn_name: str, argtypes):
+def _fn(lib_name: str, fn_name: str, argtypes, label: Optional[str] = None):
+    """The exported function, wrapped so that ``KernelTimes`` sees its launches under ``label`` (the function's
+    name without its prefix when none is given: an entry that grew an argument keeps its kernel class)."""
     key = (lib_name, fn_name)
     got = _wrapped.get(key)
     if got is not None:
@@ -141,7 +143,7 @@ def _fn(lib_name: str, fn_name: str, argtypes):
         err = getattr(lib, f"lgml_{lib_name}_last_error")
         err.restype = ctypes.c_char_p
         _prototyped.add(key)
-        _wrapped[key] = _Timed(fn, fn_name[len("lgml_"):] if fn_name.startswith("lgml_") else fn_name)
+        _wrapped[key] = _Timed(fn, label or (fn_name[len("lgml_"):] if fn_name.startswith("lgml_") else fn_name))
     return _wrapped[key]
 
 
@@ -232,7 +234,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
             raise KernelError("rmsnorm: delta must have the input's shape and be contiguous")
         ddt, dptr = dtype_code(delta.dtype), delta
     fn = _fn("elementwise", "lgml_rmsnorm_scaled", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                                    c_int, c_int, c_float, c_float, c_void_p])
+                                                    c_int, c_int, c_float, c_float, c_void_p], label="rmsnorm")
     _check("elementwise", fn(_ptr(x), _ptr(dptr), ddt, n_parts, stride, _ptr(dbias), _ptr(weight), _ptr(rows), _ptr(out),
                              dtype_code(out.dtype), n_rows, width, float(eps), float(delta_scale), _stream()), "rmsnorm")
     return out
@@ -853,7 +855,7 @@ def moe_router(h: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch
     wts = torch.empty((n, top), dtype=torch.float32, device=h.device)
     extra = torch.empty((n, n_extra), dtype=torch.float32, device=h.device) if n_extra else None
     fn = _fn("moe", "lgml_moe_router_mode", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
-                                             c_int, c_void_p, c_void_p])
+                                             c_int, c_void_p, c_void_p], label="moe_router")
     _check("moe", fn(_ptr(h), dtype_code(h.dtype), ldh, _ptr(w_router), _ptr(b_router), _ptr(ids), _ptr(wts), n, E, X, int(top), ROUTER_MODES[mode],
                      float(route_scale), int(n_extra), _ptr(extra), _stream()), "moe_router")
     return (ids, wts, extra) if n_extra else (ids, wts)
@@ -978,7 +980,7 @@ def moe_experts_tcgen05(h: torch.Tensor, ids: torch.Tensor, wts: torch.Tensor, w
                               _ptr(status), stream), "gemm_tcgen05_grouped")
     _check("gemm_tcgen05", fn(_ptr(act), _ptr(w_down), _ptr(y), 1, max_tiles, E, F, X, E, _ptr(tiles), 0, _ptr(status), stream),
            "gemm_tcgen05_grouped")
-    fn = _fn("moe", "lgml_moe_weighted_sum_also", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+    fn = _fn("moe", "lgml_moe_weighted_sum_also", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p], label="moe_weighted_sum")
     _check("moe", fn(_ptr(y), _ptr(pos), _ptr(wts), _ptr(out), n, E, top, _ptr(also), _ptr(also_w), stream), "moe_weighted_sum")
     return out
 

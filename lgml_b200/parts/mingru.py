@@ -20,7 +20,7 @@ from ..weights import VECTOR, TensorSpec
 from .base import Part, register_part
 
 # portions of a request longer than this run in pieces side by side
-MINGRU_PIECES_FROM = 128
+MINGRU_PIECES_FROM = 64
 
 
 class MinGRU(Part):

@@ -175,13 +175,15 @@ def test_mingru_in_sequence_and_in_pieces_with_gates_nearly_shut(dtype, W, E):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("E,dim,cols,col0", [(36, 5, 20, 10), (64, 12, 36, 24), (136, 24, 24, 0), (48, 1, 3, 2), (264, 64, 131, 67), (72, 264, 272, 8),
                                             (520, 8, 40, 16)])
-def test_token_input_in_one_kernel_and_as_products(dtype, E, dim, cols, col0):
+@pytest.mark.parametrize("n", [70, 3, 25, 150])
+def test_token_input_in_one_kernel_and_as_products(dtype, E, dim, cols, col0, n):
     """x += m delta; x += m rms_unit(W_proj (gelu_tanh(W_gate x) * table[token, col0 : col0 + dim])) * w, in the form
-    for few tokens (one kernel) and in the form for many (two products with small kernels between)."""
+    for few tokens (one kernel, the fewer the tokens the more blocks share one) and in the form for many (two
+    products with small kernels between)."""
     from lgml_b200 import ops
 
     torch.manual_seed(4)
-    n, vocab, m, eps = 70, 33, 0.4, 1e-5
+    vocab, m, eps = 33, 0.4, 1e-5
     x = (torch.randn(n, E, dtype=F64) * 2.0).float().double()
     delta = torch.randn(n, E, dtype=F64).float().double()
     ids = torch.randint(0, vocab, (n,))
@@ -192,11 +194,18 @@ def test_token_input_in_one_kernel_and_as_products(dtype, E, dim, cols, col0):
     want = x1 + m * torch.from_numpy(P.side_input(x1.numpy(), {k: t.numpy() for k, t in W.items()}, "s", table[ids, col0:col0 + dim].numpy(), eps))
     dev = lambda t, ty=dtype: t.to(ty).to(DEV).contiguous()
     tol = (1e-5 if dtype == torch.float32 else 4e-2) * (1.0 + float(want.abs().max()))
+    # rows whose y all but vanishes before it is divided by its root mean square are a unit vector made of rounding
+    # (with one number per token: a sign); bfloat16 is compared on the others
+    sizes = []
+    P.side_input(x1.numpy(), {k: t.numpy() for k, t in W.items()}, "s", table[ids, col0:col0 + dim].numpy(), eps, sizes)
+    sound = torch.from_numpy(sizes[0] >= (0.0 if dtype == torch.float32 else 0.1) * np.median(sizes[0]))
+    assert int(sound.sum()) >= (n + 1) // 2
+    want = want[sound]
     # one kernel
     xd = dev(x, torch.float32)
     ops.token_side(xd, dev(delta, torch.float32), m, ids.to(torch.int32).to(DEV), dev(table), col0, dev(W["s.gate"]), dev(W["s.proj"]),
                    dev(W["s.norm"], torch.float32), eps, m)
-    assert float((xd.double().cpu() - want).abs().max()) < tol
+    assert float((xd.double().cpu()[sound] - want).abs().max()) < tol
     # two products
     xd = dev(x, torch.float32)
     xb = ops.residual_fold(xd, dev(delta, torch.float32), m, copy_dtype=dtype if dtype != torch.float32 else None)
@@ -205,7 +214,7 @@ def test_token_input_in_one_kernel_and_as_products(dtype, E, dim, cols, col0):
     g = ops.side_gate(gate, ids.to(torch.int32).to(DEV), dev(table), col0, dtype)
     y = (g.float() @ dev(W["s.proj"], torch.float32).T).contiguous()
     ops.side_add(xd, y, dev(W["s.norm"], torch.float32), eps, m)
-    assert float((xd.double().cpu() - want).abs().max()) < tol
+    assert float((xd.double().cpu()[sound] - want).abs().max()) < tol
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -421,14 +430,16 @@ def test_all_cuttings_match_the_plain_model(model, dtype):
     runner = make_runner(folder, dtype, n_pages=7, slots=3)
     results["mixed"] = H.run_trace(runner, trace)
     assert all(g.pool.taken_total > g.pool.n_pages for g in runner.cache.groups if g.spec.window is None), "no page was used twice"
+    from lgml_b200.parts.mingru import MINGRU_PIECES_FROM
+
     for kind, got in results.items():
         worst = L.compare(got, cfg, weights, seqs, **TOL[dtype])
         print(f"{name} {dtype} {kind}: max |diff| {worst:.3g}")
     if dtype == "float32":
-        # portions of up to 128 tokens run the recurrence as one scan, in whichever step they come: bit-equal.  A longer
+        # short portions run the recurrence as one scan, in whichever step they come: bit-equal.  A longer
         # portion runs it in pieces (a piece's start is a product of the pieces before it), which rounds differently.
         for key, row in results["tail"].items():
-            if len(seqs[key[0]]) - 32 <= 128:
+            if len(seqs[key[0]]) - 32 <= MINGRU_PIECES_FROM:
                 assert torch.equal(row, results["portions"][key]), f"float32 portions differ from tail at {key}"
         for kind in ("tail", "portions", "mixed"):
             for key, row in results["whole"].items():
