@@ -87,7 +87,19 @@ WIDE_HEADS = config(101, 96, [
     mingru(96, mlp=moe(40, 8, 2)),
 ], eps=1e-5, mult=0.7, side=16, loop=(2, 4, 2))
 
-CONFIGS = {"looped": LOOPED, "odd": ODD, "no_side": NO_SIDE, "wide_heads": WIDE_HEADS}
+# Cells wider than any tensor-core attention kernel takes (160 and 288 numbers), a loop from the
+# first layer, a recurrence far wider than the model.
+BIG_CELLS = config(211, 72, [
+    latent(2, 16, 32, 16, 128, scale=0.2, base=10000.0, window=48, scaling=(8.0, 64, 32.0, 1.0), mlp=moe(12, 6, 2, scale=2.0, shared=20)),
+    mingru(200, mlp=dense(56)),
+    latent(3, 24, 16, 8, 272, scale=0.15, base=2000.0, window=130, mlp=dense(40)),
+], eps=1e-6, mult=0.3, side=24, loop=(0, 2, 2))
+
+# how far apart a router's choice must lie in the plain model for a bfloat16 run to be compared on a token: the wide
+# cells' scores are sums over hundreds of rounded numbers, and what comes after them wobbles more
+CLEAR_GAP = {id(BIG_CELLS): 0.05}
+
+CONFIGS = {"looped": LOOPED, "odd": ODD, "no_side": NO_SIDE, "wide_heads": WIDE_HEADS, "big_cells": BIG_CELLS}
 
 
 def random_weights(cfg: dict, seed: int, sharpen: float = 1.0) -> Dict[str, torch.Tensor]:
@@ -177,7 +189,7 @@ def oracle_logits(cfg: dict, weights: Dict[str, torch.Tensor], ids: List[int]) -
     return _oracle[key]
 
 
-def clear_ids(cfg: dict, weights: Dict[str, torch.Tensor], n: int, seed: int, gap: float = 0.02, small: float = 0.2) -> List[int]:
+def clear_ids(cfg: dict, weights: Dict[str, torch.Tensor], n: int, seed: int, gap: float = None, small: float = 0.2) -> List[int]:
     """n random token ids on which a bfloat16 run may be compared: no router of the plain model decides by less
     than ``gap`` (the choice scores are sigmoids plus a correction, so they lie close together), and no token
     input is smaller than ``small`` times that layer's median before it is divided by its root mean square (a
@@ -185,6 +197,8 @@ def clear_ids(cfg: dict, weights: Dict[str, torch.Tensor], n: int, seed: int, ga
     ahead of it).  The model is causal, so the first such position is redrawn and the sequence checked again."""
     import random
 
+    if gap is None:
+        gap = CLEAR_GAP.get(id(cfg), 0.02)
     rng = random.Random(seed)
     ids = [rng.randrange(cfg["vocab"]) for _ in range(n)]
     for _ in range(40 * n):
