@@ -49,6 +49,8 @@ LIBRARIES: Dict[str, tuple] = {
     "attention_heads": ("attention_heads.cu", []),
     "moe": ("moe.cu", []),
     "token_mix": ("token_mix.cu", []),
+    "norm_conv": ("norm_conv.cu", []),
+    "ssd": ("ssd.cu", []),
 }
 
 _HEADERS = ["common.cuh", "page_map.cuh"]

@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
     const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, const __nv_bfloat16 *__restrict__ q, int ldq,
     const int *__restrict__ positions, const int *__restrict__ tiles, const int *__restrict__ block_table, int max_blocks, int n_pages,
     __nv_bfloat16 *__restrict__ out, int ldo, int H, int Hkv, int hpc, int tt, float scale, int window, int *__restrict__ status,
-    const float *__restrict__ slopes, const float *__restrict__ sinks, const float *__restrict__ gate, int ldg) {
+    const float *__restrict__ slopes, const float *__restrict__ sinks, const float *__restrict__ gate, int ldg, float softcap) {
     constexpr int KB = D / 64;                              // 64-element blocks along the head dimension
     constexpr uint32_t TILE_BYTES = KB * ROWS * 128;        // the queries of one tile: [KB][128 rows][128 B]
     constexpr uint32_t PAGE_BYTES = KB * PAGE * 128;        // a page of keys [KB][64 keys][128 B] (K-major: row = key), or of values (N-major: 64 dims per row)
@@ -429,12 +429,23 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_attention_twin_kernel(
             if (BIAS) {
                 row_bias = -slope2 * (float)(qpos - key0);
                 const float2 scale2 = make_float2(scale_log2, scale_log2), slope22 = make_float2(slope2, slope2);
+                if (softcap > 0.f) {
+                    // capped scores: cap tanh(s / cap), tanh(u) = 1 - 2 / (2^(2 u log2 e) + 1); in base-2 units
+                    const float k1 = 2.f * scale_log2 / softcap, cap2 = softcap * 1.4426950408889634f;
 #pragma unroll
-                for (int c = 0; c < PAGE; c += 2) {
-                    const float2 x = fma2(make_float2(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2,
-                                          fma2(make_float2((float)c, (float)(c + 1)), slope22, make_float2(0.f, 0.f)));
-                    r[c] = __float_as_uint(x.x);
-                    r[c + 1] = __float_as_uint(x.y);
+                    for (int c = 0; c < PAGE; ++c) {
+                        const float e = ex2(__uint_as_float(r[c]) * k1);
+                        const float th = 1.f - __fdividef(2.f, e + 1.f);
+                        r[c] = __float_as_uint(fmaf(th, cap2, slope2 * (float)c));
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < PAGE; c += 2) {
+                        const float2 x = fma2(make_float2(__uint_as_float(r[c]), __uint_as_float(r[c + 1])), scale2,
+                                              fma2(make_float2((float)c, (float)(c + 1)), slope22, make_float2(0.f, 0.f)));
+                        r[c] = __float_as_uint(x.x);
+                        r[c + 1] = __float_as_uint(x.y);
+                    }
                 }
             }
             // (four chains each: the order of a maximum or of these float32 partial sums is a
@@ -645,7 +656,7 @@ template <int D, bool BIAS>
 int launch(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, const int *tiles, const int *block_table, int max_blocks,
            const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, __nv_bfloat16 *out, int ldo, int H, int Hkv, int hpc, int tt,
            float scale, int window, int *status, cudaStream_t stream, const float *slopes = nullptr, const float *sinks = nullptr,
-           const float *gate = nullptr, int ldg = 0) {
+           const float *gate = nullptr, int ldg = 0, float softcap = 0.f) {
     constexpr int KB = D / 64;
     const size_t smem = 2 * (size_t)KB * ROWS * 128 + 2 * STAGES * (size_t)KB * PAGE * 128 + 1024;
     static bool configured = false;
@@ -659,7 +670,7 @@ int launch(dim3 grid, const __nv_bfloat16 *q, int ldq, const int *positions, con
     if ((rc = lgml_make_page_map(&mk, k_pages, n_pages, Hkv, D, "prefill_attention_twin"))) return rc;
     if ((rc = lgml_make_page_map(&mv, v_pages, n_pages, Hkv, D, "prefill_attention_twin"))) return rc;
     lgml_launch(prefill_attention_twin_kernel<D, BIAS>, grid, THREADS, smem, stream, mk, mv, q, ldq, positions, tiles, block_table, max_blocks, n_pages,
-                out, ldo, H, Hkv, hpc, tt, scale, window, status, slopes, sinks, gate, ldg);
+                out, ldo, H, Hkv, hpc, tt, scale, window, status, slopes, sinks, gate, ldg, softcap);
     return lgml_launch_status("prefill_attention_twin");
 }
 }  // namespace
@@ -706,7 +717,7 @@ LGML_API int lgml_prefill_attention_twin(const void *q, int ldq, const int *posi
 LGML_API int lgml_sink_attention_twin(const void *q, int ldq, const int *positions, const int *tiles, int n_tiles, const int *block_table,
                                       int max_blocks, const void *k_pages, const void *v_pages, int n_pages, int page_size,
                                       const float *slopes, const float *sinks, const float *gate, int ldg, void *out, int ldo, int H, int Hkv,
-                                      int D, float scale, int window, int *status, cudaStream_t stream) {
+                                      int D, float scale, float softcap, int window, int *status, cudaStream_t stream) {
     LGML_REQUIRE(n_tiles >= 0 && H > 0 && Hkv > 0 && max_blocks > 0 && n_pages > 0, "sink_attention_twin: bad sizes");
     LGML_REQUIRE(page_size == PAGE, "sink_attention_twin: pages of %d tokens, this kernel takes %d", page_size, PAGE);
     LGML_REQUIRE(H % Hkv == 0, "sink_attention_twin: %d heads are no multiple of %d KV heads", H, Hkv);
@@ -729,7 +740,7 @@ LGML_API int lgml_sink_attention_twin(const void *q, int ldq, const int *positio
     __nv_bfloat16 *oo = (__nv_bfloat16 *)out;
     if (D == 64)
         return launch<64, true>(grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, hpc, tile_tokens / 2, scale, window,
-                                status, stream, slopes, sinks, gate, ldg);
+                                status, stream, slopes, sinks, gate, ldg, softcap);
     return launch<128, true>(grid, qq, ldq, positions, tiles, block_table, max_blocks, kk, vv, n_pages, oo, ldo, H, Hkv, hpc, tile_tokens / 2, scale, window,
-                             status, stream, slopes, sinks, gate, ldg);
+                             status, stream, slopes, sinks, gate, ldg, softcap);
 }

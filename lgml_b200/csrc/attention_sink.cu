@@ -22,6 +22,16 @@
 LGML_DEFINE_LAST_ERROR(lgml_attention_sink)
 
 namespace {
+
+// A cap on the scaled scores: cap tanh(s / cap) (cap 0: none), applied before the distance bias.
+// capped_score2 gives the result in the base-2 domain (times log2 e).
+__device__ __forceinline__ float capped_score(float dot, float scale, float cap) {
+    const float s = dot * scale;
+    return cap > 0.f ? cap * tanhf(s / cap) : s;
+}
+__device__ __forceinline__ float capped_score2(float dot, float scale, float cap) {
+    return cap * 1.4426950408889634f * tanhf(dot * scale / cap);
+}
 constexpr int ITEMS = 256;
 constexpr int WARPS = 4;
 constexpr int MAX_D = 256;        // the split decode forms (a lane holds 8 value columns)
@@ -75,7 +85,7 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
     const T *__restrict__ q, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token,
     const int *__restrict__ block_table, int max_blocks, const T *__restrict__ k_pages, const T *__restrict__ v_pages,
     int n_pages, int page_size, const float *__restrict__ slopes, const float *__restrict__ sinks,
-    const float *__restrict__ gate, int ldg, TO *__restrict__ out, int ldo, int H, int Hkv, int Hv, int D, int Dv, int ldv, float scale,
+    const float *__restrict__ gate, int ldg, TO *__restrict__ out, int ldo, int H, int Hkv, int Hv, int D, int Dv, int ldv, float scale, float softcap,
     int window, int keep_first, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
@@ -115,7 +125,7 @@ __global__ void __launch_bounds__(WARPS * 32) sink_attention_kernel(
         const size_t vcell = ((size_t)page * Hv + gv) * page_size + (size_t)(j % page_size);
         float dot = 0.f;
         for (int d = lane; d < D; d += 32) dot = fmaf(qs[d], to_f32(act_load(k_pages + cell * D + d)), dot);
-        const float s = warp_sum(dot) * scale - slope * (float)(pos - j);
+        const float s = capped_score(warp_sum(dot), scale, softcap) - slope * (float)(pos - j);
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);  // exp(-inf) = 0 on the first key
         const float p = expf(s - m_new);
@@ -229,7 +239,7 @@ __global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, const float *__restrict__ slopes, const float *__restrict__ sinks,
     const float *__restrict__ gate, int ldg, void *__restrict__ out, int out_f32, int ldo, int H, int Hkv, int Hv, int D, int Dv, int ldv,
-    float scale, int window, int keep_first, int *__restrict__ status) {
+    float scale, float softcap, int window, int keep_first, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
     constexpr int DP = KS * 16, DVP = NV * 8;
@@ -350,7 +360,8 @@ __global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
             for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float sv = fmaf(sacc[nt][i], scale2, rowt[i >> 1] + fmaf(slope2, (float)(nt * 8 + (i & 1)), colb));
+                    const float bias2 = rowt[i >> 1] + fmaf(slope2, (float)(nt * 8 + (i & 1)), colb);
+                    const float sv = softcap > 0.f ? capped_score2(sacc[nt][i], scale, softcap) + bias2 : fmaf(sacc[nt][i], scale2, bias2);
                     sacc[nt][i] = sv;
                     mx[i >> 1] = fmaxf(mx[i >> 1], sv);
                 }
@@ -363,7 +374,7 @@ __global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
                     const int j = key0 + nt * 8 + (lane & 3) * 2 + (i & 1);
                     const int dist = qpos[rr] - j;
                     const bool ok = qok[rr] && dist >= 0 && (window == 0 || dist < window || j < keep_first);
-                    const float sv = ok ? sacc[nt][i] * scale2 - slope2 * (float)dist : -INFINITY;
+                    const float sv = ok ? (softcap > 0.f ? capped_score2(sacc[nt][i], scale, softcap) : sacc[nt][i] * scale2) - slope2 * (float)dist : -INFINITY;
                     sacc[nt][i] = sv;
                     mx[rr] = fmaxf(mx[rr], sv);
                 }
@@ -436,7 +447,7 @@ __global__ void __launch_bounds__(128, 3) sink_attention_mma_kernel(
 template <int KS, int NV>
 int launch_mma(dim3 grid, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, const int *positions, const int *tiles, const int *block_table,
                int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages, const float *slopes, const float *sinks,
-               const float *gate, int ldg, void *out, int out_f32, int ldo, int H, int Hkv, int Hv, int D, int Dv, int ldv, float scale, int window,
+               const float *gate, int ldg, void *out, int out_f32, int ldo, int H, int Hkv, int Hv, int D, int Dv, int ldv, float scale, float softcap, int window,
                int keep_first, int *status) {
     const size_t smem = ((size_t)2 * PAGE * (KS * 16 + 8) + (size_t)2 * PAGE * (NV * 8 + 8)) * 2;
     if (smem > 48 * 1024) {
@@ -444,7 +455,7 @@ int launch_mma(dim3 grid, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, 
         if (e != cudaSuccess) LGML_FAIL("sink_attention_mma: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
     lgml_launch(sink_attention_mma_kernel<KS, NV>, grid, 128, smem, stream, q, ldq, positions, tiles, block_table, max_blocks, k_pages, v_pages,
-                n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, H, Hkv, Hv, D, Dv, ldv, scale, window, keep_first, status);
+                n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, H, Hkv, Hv, D, Dv, ldv, scale, softcap, window, keep_first, status);
     return lgml_launch_status("sink_attention_mma");
 }
 
@@ -470,7 +481,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_kernel(
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, const float *__restrict__ slopes, const float *__restrict__ sinks,
     const float *__restrict__ gate, int ldg, void *__restrict__ out, int out_f32, int ldo, float *__restrict__ part_o,
-    float2 *__restrict__ part_ml, int n_splits, int n_chunks, int H, int Hkv, int Hv, int D, int Dv, int ldv, float scale, int window,
+    float2 *__restrict__ part_ml, int n_splits, int n_chunks, int H, int Hkv, int Hv, int D, int Dv, int ldv, float scale, float softcap, int window,
     int keep_first, int v_stage, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
@@ -590,7 +601,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_kernel(
         float corr[GH];
 #pragma unroll
         for (int hh = 0; hh < GH; ++hh) {
-            const float sv = ok ? sc[hh] * scale2 - slope2[hh] * (float)(pos - j) : -INFINITY;
+            const float sv = ok ? (softcap > 0.f ? capped_score2(sc[hh], scale, softcap) : sc[hh] * scale2) - slope2[hh] * (float)(pos - j) : -INFINITY;
             const float m_new = fmaxf(m_run[hh], warp_max(sv));
             corr[hh] = (m_new == -INFINITY) ? 1.f : exp2f(m_run[hh] - m_new);
             const float p = (m_new == -INFINITY) ? 0.f : exp2f(sv - m_new);
@@ -770,7 +781,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_mma_kernel(
     const int *__restrict__ block_table, int max_blocks, const __nv_bfloat16 *__restrict__ k_pages,
     const __nv_bfloat16 *__restrict__ v_pages, int n_pages, const float *__restrict__ slopes, const float *__restrict__ sinks,
     const float *__restrict__ gate, int ldg, void *__restrict__ out, int out_f32, int ldo, float *__restrict__ part_o,
-    float2 *__restrict__ part_ml, int n_splits, int H, int Hkv, int Hv, int ldv, int heads_per_cta, int n_chunks, float scale, int window,
+    float2 *__restrict__ part_ml, int n_splits, int H, int Hkv, int Hv, int ldv, int heads_per_cta, int n_chunks, float scale, float softcap, int window,
     int keep_first, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
@@ -877,7 +888,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) sink_decode_mma_kernel(
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int kpos = key_base + (lane >> 2) + (i >> 1) * 8;
-            c[i] = ((kpos >= lo || kpos < keep_first) && kpos <= pos) ? c[i] * scale2 - slope2[i & 1] * (float)(pos - kpos) : -INFINITY;
+            c[i] = ((kpos >= lo || kpos < keep_first) && kpos <= pos)
+                       ? (softcap > 0.f ? capped_score2(c[i], scale, softcap) : c[i] * scale2) - slope2[i & 1] * (float)(pos - kpos) : -INFINITY;
             mx[i & 1] = fmaxf(mx[i & 1], c[i]);
         }
         float corr[2];
@@ -968,7 +980,7 @@ template <int KS, int VS>
 int launch_decode_mma(dim3 grid, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token,
                       const int *block_table, int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages,
                       const float *slopes, const float *sinks, const float *gate, int ldg, void *out, int out_f32, int ldo, float *part_o,
-                      float2 *part_ml, int n_splits, int H, int Hkv, int Hv, int ldv, int heads_per_cta, int n_chunks, float scale, int window,
+                      float2 *part_ml, int n_splits, int H, int Hkv, int Hv, int ldv, int heads_per_cta, int n_chunks, float scale, float softcap, int window,
                       int keep_first, int *status) {
     constexpr int STAGES = 3;
     constexpr int D = KS * 16, DV = VS * 16;
@@ -981,7 +993,7 @@ int launch_decode_mma(dim3 grid, cudaStream_t stream, const __nv_bfloat16 *q, in
     }
     lgml_launch(sink_decode_mma_kernel<KS, VS, STAGES>, grid, DEC_WARPS * 32, smem, stream, q, ldq, positions, seq_of_token, block_table, max_blocks,
                 k_pages, v_pages, n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, part_o, part_ml, n_splits, H, Hkv, Hv, ldv, heads_per_cta,
-                n_chunks, scale, window, keep_first, status);
+                n_chunks, scale, softcap, window, keep_first, status);
     return lgml_launch_status("sink_decode_mma");
 }
 
@@ -989,14 +1001,14 @@ template <int GH, bool VEC>
 int launch_decode(dim3 grid, size_t smem, cudaStream_t stream, const __nv_bfloat16 *q, int ldq, const int *positions, const int *seq_of_token,
                   const int *block_table, int max_blocks, const __nv_bfloat16 *k_pages, const __nv_bfloat16 *v_pages, int n_pages,
                   const float *slopes, const float *sinks, const float *gate, int ldg, void *out, int out_f32, int ldo, float *part_o,
-                  float2 *part_ml, int n_splits, int n_chunks, int H, int Hkv, int Hv, int D, int Dv, int ldv, float scale, int window,
+                  float2 *part_ml, int n_splits, int n_chunks, int H, int Hkv, int Hv, int D, int Dv, int ldv, float scale, float softcap, int window,
                   int keep_first, int v_stage, int *status) {
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(sink_decode_kernel<GH, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) LGML_FAIL("sink_decode: cannot have %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     }
     lgml_launch(sink_decode_kernel<GH, VEC>, grid, DEC_WARPS * 32, smem, stream, q, ldq, positions, seq_of_token, block_table, max_blocks, k_pages,
-                v_pages, n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, part_o, part_ml, n_splits, n_chunks, H, Hkv, Hv, D, Dv, ldv, scale, window,
+                v_pages, n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, part_o, part_ml, n_splits, n_chunks, H, Hkv, Hv, D, Dv, ldv, scale, softcap, window,
                 keep_first, v_stage, status);
     return lgml_launch_status("sink_decode");
 }
@@ -1039,7 +1051,7 @@ LGML_API int lgml_sink_qkv_store(const float *proj, int ldp, void *q_out, int dt
 LGML_API int lgml_sink_attention(const void *q, int dtype, int ldq, const int *positions, const int *seq_of_token, const int *block_table,
                                  int max_blocks, const void *k_pages, const void *v_pages, int n_pages, int page_size, const float *slopes,
                                  const float *sinks, const float *gate, int ldg, void *out, int out_dtype, int ldo, int n_tokens, int H, int Hkv,
-                                 int Hv, int D, int Dv, int ldv, float scale, int window, int keep_first, int *status, cudaStream_t stream) {
+                                 int Hv, int D, int Dv, int ldv, float scale, float softcap, int window, int keep_first, int *status, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && Hv > 0 && D > 0 && Dv > 0 && page_size > 0 && max_blocks > 0, "sink_attention: bad sizes");
     LGML_REQUIRE(H % Hkv == 0, "sink_attention: %d heads are no multiple of %d KV heads", H, Hkv);
     LGML_REQUIRE(Hkv % Hv == 0, "sink_attention: %d key heads are no multiple of %d value heads", Hkv, Hv);
@@ -1054,15 +1066,15 @@ LGML_API int lgml_sink_attention(const void *q, int dtype, int ldq, const int *p
     if (dtype == LGML_F32)
         lgml_launch(sink_attention_kernel<float, float>, grid, WARPS * 32, 0, stream, (const float *)q, ldq, positions, seq_of_token, block_table,
                     max_blocks, (const float *)k_pages, (const float *)v_pages, n_pages, page_size, slopes, sinks, gate, ldg, (float *)out, ldo, H,
-                    Hkv, Hv, D, Dv, ldv, scale, window, keep_first, status);
+                    Hkv, Hv, D, Dv, ldv, scale, softcap, window, keep_first, status);
     else if (dtype == LGML_BF16 && out_dtype == LGML_F32)
         lgml_launch(sink_attention_kernel<__nv_bfloat16, float>, grid, WARPS * 32, 0, stream, (const __nv_bfloat16 *)q, ldq, positions, seq_of_token,
                     block_table, max_blocks, (const __nv_bfloat16 *)k_pages, (const __nv_bfloat16 *)v_pages, n_pages, page_size, slopes, sinks,
-                    gate, ldg, (float *)out, ldo, H, Hkv, Hv, D, Dv, ldv, scale, window, keep_first, status);
+                    gate, ldg, (float *)out, ldo, H, Hkv, Hv, D, Dv, ldv, scale, softcap, window, keep_first, status);
     else if (dtype == LGML_BF16)
         lgml_launch(sink_attention_kernel<__nv_bfloat16, __nv_bfloat16>, grid, WARPS * 32, 0, stream, (const __nv_bfloat16 *)q, ldq, positions, seq_of_token,
                     block_table, max_blocks, (const __nv_bfloat16 *)k_pages, (const __nv_bfloat16 *)v_pages, n_pages, page_size, slopes, sinks,
-                    gate, ldg, (__nv_bfloat16 *)out, ldo, H, Hkv, Hv, D, Dv, ldv, scale, window, keep_first, status);
+                    gate, ldg, (__nv_bfloat16 *)out, ldo, H, Hkv, Hv, D, Dv, ldv, scale, softcap, window, keep_first, status);
     else
         LGML_FAIL("sink_attention: unknown type %d", dtype);
     return lgml_launch_status("sink_attention");
@@ -1074,7 +1086,7 @@ LGML_API int lgml_sink_attention(const void *q, int dtype, int ldq, const int *p
 LGML_API int lgml_sink_attention_mma(const void *q, int ldq, const int *positions, const int *tiles, int n_tiles, const int *block_table,
                                      int max_blocks, const void *k_pages, const void *v_pages, int n_pages, int page_size,
                                      const float *slopes, const float *sinks, const float *gate, int ldg, void *out, int out_f32, int ldo, int H,
-                                     int Hkv, int Hv, int D, int Dv, int ldv, float scale, int window, int keep_first, int *status,
+                                     int Hkv, int Hv, int D, int Dv, int ldv, float scale, float softcap, int window, int keep_first, int *status,
                                      cudaStream_t stream) {
     LGML_REQUIRE(n_tiles >= 0 && H > 0 && Hkv > 0 && Hv > 0 && D > 0 && Dv > 0 && max_blocks > 0, "sink_attention_mma: bad sizes");
     LGML_REQUIRE(Hkv % Hv == 0 && ldv >= Dv && keep_first >= 0, "sink_attention_mma: %d key heads on %d value heads, value rows %d apart", Hkv, Hv, ldv);
@@ -1088,7 +1100,7 @@ LGML_API int lgml_sink_attention_mma(const void *q, int ldq, const int *position
     const int ks = D <= 32 ? 2 : D <= 64 ? 4 : D <= 96 ? 6 : 8;
     const int nv = Dv <= 32 ? 4 : Dv <= 64 ? 8 : Dv <= 96 ? 12 : 16;
 #define LGML_MMA_ARGS grid, stream, (const __nv_bfloat16 *)q, ldq, positions, tiles, block_table, max_blocks, (const __nv_bfloat16 *)k_pages, \
-                      (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, H, Hkv, Hv, D, Dv, ldv, scale, window, \
+                      (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, H, Hkv, Hv, D, Dv, ldv, scale, softcap, window, \
                       keep_first, status
 #define LGML_MMA_NV(KK) \
     switch (nv) { case 4: return launch_mma<KK, 4>(LGML_MMA_ARGS); case 8: return launch_mma<KK, 8>(LGML_MMA_ARGS); \
@@ -1109,7 +1121,7 @@ LGML_API int lgml_sink_attention_mma(const void *q, int ldq, const int *position
 LGML_API int lgml_sink_decode(const void *q, int ldq, const int *positions, const int *seq_of_token, const int *block_table, int max_blocks,
                               const void *k_pages, const void *v_pages, int n_pages, int page_size, const float *slopes, const float *sinks,
                               const float *gate, int ldg, void *out, int out_f32, int ldo, float *scratch, int n_splits, int n_tokens, int H,
-                              int Hkv, int Hv, int D, int Dv, int ldv, float scale, int window, int keep_first, int *status, cudaStream_t stream) {
+                              int Hkv, int Hv, int D, int Dv, int ldv, float scale, float softcap, int window, int keep_first, int *status, cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && H > 0 && Hkv > 0 && Hv > 0 && D > 0 && Dv > 0 && max_blocks > 0, "sink_decode: bad sizes");
     LGML_REQUIRE(Hkv % Hv == 0 && ldv >= Dv && keep_first >= 0, "sink_decode: %d key heads on %d value heads, value rows %d apart", Hkv, Hv, ldv);
     LGML_REQUIRE(page_size == PAGE, "sink_decode: pages of %d tokens, this kernel takes %d", page_size, PAGE);
@@ -1133,7 +1145,7 @@ LGML_API int lgml_sink_decode(const void *q, int ldq, const int *positions, cons
         int rc = 0;
 #define LGML_DM_ARGS grid, stream, (const __nv_bfloat16 *)q, ldq, positions, seq_of_token, block_table, max_blocks, (const __nv_bfloat16 *)k_pages, \
                      (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, part_o, part_ml, n_splits, H, Hkv, Hv, ldv, \
-                     heads_per_cta, n_chunks, scale, window, keep_first, status
+                     heads_per_cta, n_chunks, scale, softcap, window, keep_first, status
 #define LGML_DM_VS(KK) \
     switch (Dv / 16) { case 2: rc = launch_decode_mma<KK, 2>(LGML_DM_ARGS); break; case 4: rc = launch_decode_mma<KK, 4>(LGML_DM_ARGS); break; \
                        case 6: rc = launch_decode_mma<KK, 6>(LGML_DM_ARGS); break; default: rc = launch_decode_mma<KK, 8>(LGML_DM_ARGS); break; } \
@@ -1163,7 +1175,7 @@ LGML_API int lgml_sink_decode(const void *q, int ldq, const int *positions, cons
     int rc;
 #define LGML_DEC_ARGS grid, smem, stream, (const __nv_bfloat16 *)q, ldq, positions, seq_of_token, block_table, max_blocks, (const __nv_bfloat16 *)k_pages, \
                       (const __nv_bfloat16 *)v_pages, n_pages, slopes, sinks, gate, ldg, out, out_f32, ldo, part_o, part_ml, n_splits, n_chunks, H, \
-                      Hkv, Hv, D, Dv, ldv, scale, window, keep_first, v_stage, status
+                      Hkv, Hv, D, Dv, ldv, scale, softcap, window, keep_first, v_stage, status
 #define LGML_DEC_GH(G) rc = vec ? launch_decode<G, true>(LGML_DEC_ARGS) : launch_decode<G, false>(LGML_DEC_ARGS); break;
     switch (gh) {
         case 8: LGML_DEC_GH(8)

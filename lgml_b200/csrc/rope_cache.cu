@@ -239,6 +239,111 @@ int launch(const void *src, int lds, int n_parts, long long part_stride, const f
                                                             (T *)v_pages, n_pages, page_size, H, Hkv, D, write_kv, status);
     return lgml_launch_status("rope_kv_write");
 }
+// ---------------------------------------------------------------------------------------------
+// conv_rope_store: q and k pass a short causal convolution over time per channel, the values are
+// the convolved keys as they are (their first Dv entries), then q and k turn by their positions
+// (pairs (i, i + n_rot / 2) of the first n_rot entries; cos and sin times `mag`), k and v go to
+// their cells, q to its buffer.
+//   proj float32 [n, ldp]: q at column 0 (H D), k behind it (G D); wT float32 [taps, (H + G) D] (row j weighs the
+//   input taps - 1 - j tokens back); state: per slot (taps - 1) x (H + G) D floats, the oldest input first.
+// One work item = one rotated pair, or one entry past n_rot, of one head of one token.  The tokens that reach back
+// before the step's first token of their request are all computed by the item of that first token, which then
+// writes the slot (no other item touches its floats there).
+constexpr int CONV_MAX_TAPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(ITEMS) conv_rope_store_kernel(
+    const float *__restrict__ proj, int ldp, const float *__restrict__ wT, float *__restrict__ state, long long state_ld, int taps,
+    T *__restrict__ q_out, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token, const int *__restrict__ seq_start,
+    const int *__restrict__ slots, const int *__restrict__ block_table, int max_blocks, const float *__restrict__ inv_freq,
+    const float *__restrict__ inv_freq_lo, float mag, int n_rot, T *__restrict__ k_pages, T *__restrict__ v_pages, int n_pages, int page_size,
+    int H, int G, int D, int Dv, int write_kv, int *__restrict__ status) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int half_rot = n_rot / 2, iph = half_rot + (D - n_rot);
+    const int n_heads = write_kv ? H + G : H;
+    const int item = blockIdx.y * ITEMS + threadIdx.x;
+    if (item >= n_heads * iph) return;
+    const int head = item / iph, j = item - head * iph;
+    const int s = seq_of_token[t];
+    const int t0 = seq_start[s];
+    const int i = t - t0, back = taps - 1;
+    if (i > 0 && i < back) return;
+    const int d0 = j < half_rot ? j : n_rot + (j - half_rot);
+    const int d1 = j < half_rot ? j + half_rot : -1;
+    const bool two = d1 >= 0;
+    const float f = two ? inv_freq[j] : 0.f, f_lo = (two && inv_freq_lo) ? inv_freq_lo[j] : 0.f;
+    const int C = (H + G) * D;
+    const int c0 = head * D + d0, c1 = head * D + (two ? d1 : d0);
+    float w0[CONV_MAX_TAPS], w1[CONV_MAX_TAPS];
+    for (int k = 0; k < taps; ++k) w0[k] = __ldg(wT + (size_t)k * C + c0), w1[k] = __ldg(wT + (size_t)k * C + c1);
+
+    auto emit = [&](int tt, float a, float b) {
+        const int pos = positions[tt];
+        float ra = a, rb = b;
+        if (two) {
+            float sn, cs;
+            rope_sincos(pos, f, f_lo, &sn, &cs);
+            sn *= mag, cs *= mag;
+            ra = a * cs - b * sn;
+            rb = b * cs + a * sn;
+        }
+        if (head < H) {
+            T *qr = q_out + (size_t)tt * ldq + (size_t)head * D;
+            qr[d0] = from_f32<T>(ra);
+            if (two) qr[d1] = from_f32<T>(rb);
+            return;
+        }
+        const int g = head - H;
+        const int blk = pos / page_size;
+        int page = -1;
+        if (pos >= 0 && blk < max_blocks) page = block_table[(size_t)s * max_blocks + blk];
+        if (page < 0 || page >= n_pages) {       // the host reserves pages first; never write outside the pool
+            if (j == 0) atomicExch(status, 2);
+            return;
+        }
+        const size_t cell = ((size_t)page * G + g) * page_size + (size_t)(pos % page_size);
+        k_pages[cell * D + d0] = from_f32<T>(ra);
+        if (two) k_pages[cell * D + d1] = from_f32<T>(rb);
+        if (d0 < Dv) v_pages[cell * Dv + d0] = from_f32<T>(a);
+        if (two && d1 < Dv) v_pages[cell * Dv + d1] = from_f32<T>(b);
+    };
+
+    if (i >= back) {
+        float a = 0.f, b = 0.f;
+        for (int k = 0; k < taps; ++k) {
+            const float *row = proj + (size_t)(t - back + k) * ldp;
+            a = fmaf(w0[k], act_load(row + c0), a);
+            if (two) b = fmaf(w1[k], act_load(row + c1), b);
+        }
+        emit(t, a, b);
+        return;
+    }
+    const int n_s = seq_start[s + 1] - t0;
+    float *st = state + (size_t)slots[s] * state_ld;
+    float old0[CONV_MAX_TAPS], old1[CONV_MAX_TAPS];
+    for (int r = 0; r < back; ++r) old0[r] = act_load(st + (size_t)r * C + c0), old1[r] = two ? act_load(st + (size_t)r * C + c1) : 0.f;
+    const int first = n_s < back ? n_s : back;
+    for (int kk = 0; kk < first; ++kk) {
+        float a = 0.f, b = 0.f;
+        for (int k = 0; k < taps; ++k) {
+            const int rel = kk - back + k;
+            const float u0 = rel >= 0 ? act_load(proj + (size_t)(t0 + rel) * ldp + c0) : old0[back + rel];
+            a = fmaf(w0[k], u0, a);
+            if (two) {
+                const float u1 = rel >= 0 ? act_load(proj + (size_t)(t0 + rel) * ldp + c1) : old1[back + rel];
+                b = fmaf(w1[k], u1, b);
+            }
+        }
+        emit(t0 + kk, a, b);
+    }
+    for (int r = 0; r < back; ++r) {
+        const int rel = n_s - back + r;
+        st[(size_t)r * C + c0] = rel >= 0 ? act_load(proj + (size_t)(t0 + rel) * ldp + c0) : old0[back + rel];
+        if (two) st[(size_t)r * C + c1] = rel >= 0 ? act_load(proj + (size_t)(t0 + rel) * ldp + c1) : old1[back + rel];
+    }
+}
 }  // namespace
 
 // src: [n_parts][n_tokens][(H + 2 Hkv) D] of src_dtype (row stride lds, part_stride elements between
@@ -273,4 +378,31 @@ LGML_API int lgml_rope_kv_write(const void *src, int src_dtype, int lds, int n_p
     }
 #undef ARGS
     LGML_FAIL("rope_kv_write: unsupported types (source %d, output %d)", src_dtype, dtype);
+}
+
+
+// q and k through a short convolution (taps >= 1; 1: none, w is then one row), the values are the convolved keys'
+// first Dv entries, rotation of the first n_rot entries of q and k with cos and sin times mag; see the kernel.
+LGML_API int lgml_conv_rope_store(const float *proj, int ldp, const float *wT, float *state, long long state_ld, int taps, void *q_out, int dtype,
+                                  int ldq, const int *positions, const int *seq_of_token, const int *seq_start, const int *slots,
+                                  const int *block_table, int max_blocks, const float *inv_freq, const float *inv_freq_lo, float mag, int n_rot,
+                                  void *k_pages, void *v_pages, int n_pages, int page_size, int n_tokens, int H, int G, int D, int Dv, int write_kv,
+                                  int *status, cudaStream_t stream) {
+    LGML_REQUIRE(n_tokens >= 0 && H > 0 && G > 0 && D > 0 && Dv > 0 && Dv <= D && page_size > 0 && max_blocks > 0, "conv_rope_store: bad sizes");
+    LGML_REQUIRE(n_rot >= 0 && n_rot <= D && n_rot % 2 == 0, "conv_rope_store: n_rot %d must be even and at most the head size %d", n_rot, D);
+    LGML_REQUIRE(taps >= 1 && taps <= CONV_MAX_TAPS, "conv_rope_store: 1 to %d taps, not %d", CONV_MAX_TAPS, taps);
+    LGML_REQUIRE(taps == 1 || (state != nullptr && state_ld >= (long long)(taps - 1) * (H + G) * D), "conv_rope_store: the state's rows are too short");
+    LGML_REQUIRE(ldp >= (H + G) * D && ldq >= H * D, "conv_rope_store: rows too short");
+    if (n_tokens == 0) return 0;
+    const int iph = n_rot / 2 + (D - n_rot);
+    const int items = (write_kv ? H + G : H) * iph;
+    dim3 grid(n_tokens, (items + ITEMS - 1) / ITEMS);
+#define LGML_CRS(T) lgml_launch(conv_rope_store_kernel<T>, grid, ITEMS, 0, stream, proj, ldp, wT, state, state_ld, taps, (T *)q_out, ldq, positions, \
+                                seq_of_token, seq_start, slots, block_table, max_blocks, inv_freq, inv_freq_lo, mag, n_rot, (T *)k_pages, (T *)v_pages, \
+                                n_pages, page_size, H, G, D, Dv, write_kv, status)
+    if (dtype == LGML_F32) LGML_CRS(float);
+    else if (dtype == LGML_BF16) LGML_CRS(__nv_bfloat16);
+    else LGML_FAIL("conv_rope_store: unknown type %d", dtype);
+#undef LGML_CRS
+    return lgml_launch_status("conv_rope_store");
 }

@@ -112,11 +112,13 @@ class Runtime:
                                            out, n_heads, scale, window, self.status, softcap=softcap)
         return ops.paged_attention(q, batch, cache, out, n_heads, scale, window, self.status)
 
-    def sink_attention(self, q, batch, cache, out, n_heads: int, scale: float, window: int, slopes, sinks, gate, keep_first: int = 0) -> torch.Tensor:
+    def sink_attention(self, q, batch, cache, out, n_heads: int, scale: float, window: int, slopes, sinks, gate, keep_first: int = 0,
+                       softcap: float = 0.0) -> torch.Tensor:
         """Attention with a sink, distance slopes, a window (beyond which a request's first
         ``keep_first`` tokens stay visible) and an output gate, of the step's queries over the
         cache.  Keys and values have head sizes of their own; the values may have fewer heads
-        than the keys, or be the first entries of the key cells."""
+        than the keys, or be the first entries of the key cells.  ``softcap`` > 0 caps the scaled scores:
+        s -> softcap tanh(s / softcap)."""
         bf16 = self.dtype == torch.bfloat16 and self.attention_backend != "ref" and cache.k.shape[2] == 64
         # what only this family's own kernels know: kept first tokens, value heads of their own count, values that are a
         # column range of the key cells, a float32 result
@@ -127,20 +129,20 @@ class Runtime:
                 hkv = cache.k.shape[1]
                 tiles = batch.attention_tiles(ops.prefill_twin_tile_tokens(n_heads, hkv))
                 return ops.sink_attention_twin(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window,
-                                               self.status, slopes=slopes, sinks=sinks, gate=gate)
+                                               self.status, slopes=slopes, sinks=sinks, gate=gate, softcap=softcap)
             # every other head size up to 128: tiles of 64 tokens, mma.sync
             tiles = batch.attention_tiles(ops.SINK_TILE_TOKENS)
             return ops.sink_attention_mma(q, batch.positions, tiles, cache.block_table, cache.k, cache.v, out, n_heads, scale, window,
-                                          self.status, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first)
+                                          self.status, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first, softcap=softcap)
         if bf16 and cache.k.shape[3] <= 256 and cache.v.shape[3] <= 256:
             # decoding and short portions (and prompts of head sizes beyond 128): every token's keys in ranges, the heads of a KV head together
             hkv = cache.k.shape[1]
             reach = (min(window, batch.max_kv_len) if window else batch.max_kv_len) + (keep_first if window else 0)
             n_splits = ops.sink_decode_splits(q.shape[0], hkv, n_heads // hkv, reach)
             return ops.sink_decode(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale, window,
-                                   self.status, n_splits, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first)
+                                   self.status, n_splits, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first, softcap=softcap)
         return ops.sink_attention(q, batch.positions, batch.seq_of_token, cache.block_table, cache.k, cache.v, out, n_heads, scale,
-                                  window, self.status, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first)
+                                  window, self.status, slopes=slopes, sinks=sinks, gate=gate, keep_first=keep_first, softcap=softcap)
 
     # ---- mixture of experts ------------------------------------------------------------
     def moe_experts(self, h, ids, wts, w_gu, w_down, gated: bool = True, also=None, also_w=None) -> torch.Tensor:

@@ -5,6 +5,7 @@ from . import llama  # noqa: F401  (registers LlamaForCausalLM)
 from . import lefulorn  # noqa: F401  (registers Lefulorn)
 from . import gotulorn  # noqa: F401  (registers Gotulorn)
 from . import konovik  # noqa: F401  (registers Konovik)
+from . import dizepel  # noqa: F401  (registers Dizepel)
 
 
 def build_model(config):

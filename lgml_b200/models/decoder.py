@@ -13,13 +13,15 @@ whose logits are wanted (``:2349-2350``), the final norm and the head
 """
 from __future__ import annotations
 
+import dataclasses
 from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
 import torch
 
 from .. import ops
-from ..weights import TensorSpec
+from ..parts.norm import PendingDelta, UnitMix
+from ..weights import VECTOR, TensorSpec
 
 
 @dataclass(frozen=True)
@@ -27,6 +29,7 @@ class LayerCall:
     block: int                    # index into DecoderModel.blocks
     cache: Optional[int] = None   # index of the call that owns the cache used; None = this call
     add_input: bool = False       # the residual stream as it was before the first call is added to it before this call
+    add_row: Optional[int] = None  # this row of the model's table of pass vectors is added to every token's x before this call
 
 
 class DecoderModel:
@@ -34,10 +37,12 @@ class DecoderModel:
                  block_prefix: str = "model.layers.{}", final_norm_prefix: str = "model.norm",
                  embed_scale: Optional[float] = None, logit_scale: Optional[float] = None, logit_softcap: Optional[float] = None,
                  ignored_tensors: Sequence[str] = (), embed_norm=None, embed_norm_prefix: str = "model.embed_norm",
-                 delta_dtype: Optional[torch.dtype] = None):
+                 delta_dtype: Optional[torch.dtype] = None, pass_rows: Optional[str] = None):
         self.config = config
         # the type in which mixers and feed-forwards hand their results to the residual stream (None: the compute type)
         self.delta_dtype = delta_dtype
+        # the name of a tensor [rows, width] whose rows schedule entries add to x (``LayerCall.add_row``)
+        self.pass_rows_name, self.pass_rows = pass_rows, None
         self.embedding = embedding
         self.blocks = list(blocks)
         self.final_norm = final_norm
@@ -61,6 +66,9 @@ class DecoderModel:
                     raise ValueError(f"schedule entry {ci} reads the cache of entry {call.cache}, which does not run before it")
                 if self.schedule[call.cache].cache is not None:
                     raise ValueError(f"schedule entry {ci} reads the cache of entry {call.cache}, which has none of its own")
+            if call.add_row is not None and pass_rows is None:
+                raise ValueError(f"schedule entry {ci} adds a pass vector, but the model names no table of them")
+        self.n_pass_rows = 1 + max((call.add_row for call in self.schedule if call.add_row is not None), default=-1)
         self.vocab_size = head.vocab
         parts = [embedding, final_norm, head] + self.blocks + ([embed_norm] if embed_norm is not None else [])
         self.graph_safe = all(getattr(p, "graph_safe", False) for p in parts)
@@ -75,6 +83,8 @@ class DecoderModel:
             specs += b.tensor_specs(self.block_prefix.format(i))
         specs += self.final_norm.tensor_specs(self.final_norm_prefix)
         specs += self.head.tensor_specs("")
+        if self.pass_rows_name is not None and self.n_pass_rows:
+            specs.append(TensorSpec(self.pass_rows_name, (self.n_pass_rows, self.embedding.width), VECTOR))
         seen = {}
         for s in specs:          # a tensor two parts share (e.g. frequency factors) is listed once
             seen.setdefault(s.name, s)
@@ -88,6 +98,8 @@ class DecoderModel:
             b.bind(self.block_prefix.format(i), tensors, rt)
         self.final_norm.bind(self.final_norm_prefix, tensors, rt)
         self.head.bind("", tensors, rt)
+        if self.pass_rows_name is not None and self.n_pass_rows:
+            self.pass_rows = tensors[self.pass_rows_name].float().contiguous()
 
     # ---- cache -------------------------------------------------------------------------
     def cache_layout(self) -> Dict[int, object]:
@@ -99,6 +111,29 @@ class DecoderModel:
                 if spec is not None:
                     out[ci] = spec
         return out
+
+    @staticmethod
+    def _with_row(x, pending, row, block):
+        """What is pending for x once ``row`` is to be added to every token's x as well: a block whose first norm takes
+        such a delta gets it with the row; for any other the sums are made here."""
+        if getattr(block, "takes_pending_row", False) and (pending is None or (isinstance(pending, PendingDelta) and pending.row_add is None)):
+            return dataclasses.replace(pending, row_add=row) if pending is not None else PendingDelta(row_add=row)
+        DecoderModel._fold(x, pending)
+        ops.sandwich_norm(x, None, 0.0, None, row_add=row)
+        return None
+
+    @staticmethod
+    def _fold(x, pending) -> None:
+        """x += what is pending, now, by a kernel of its own."""
+        if isinstance(pending, PendingDelta):
+            d = pending.delta
+            if isinstance(d, UnitMix):
+                ops.sandwich_norm(x, None, pending.eps, None, delta=(d.a, d.b), units=(d.u_a, d.u_b), w_post=pending.w_post, row_add=pending.row_add)
+            else:
+                ops.sandwich_norm(x, None, pending.eps, None, delta=d.sum() if isinstance(d, ops.Partials) else d, w_post=pending.w_post,
+                                  row_add=pending.row_add)
+        elif pending is not None:
+            ops.residual_fold(x, pending)
 
     # ---- the forward pass of one step --------------------------------------------------
     def forward(self, rt, batch) -> torch.Tensor:
@@ -114,9 +149,11 @@ class DecoderModel:
         for ci, call in enumerate(self.schedule):
             if call.add_input:
                 if pending is not None:
-                    ops.residual_fold(x, pending)
+                    self._fold(x, pending)
                     pending = None
                 ops.residual_fold(x, x_in)
+            if call.add_row is not None:
+                pending = self._with_row(x, pending, self.pass_rows[call.add_row], self.blocks[call.block])
             owner = ci if call.cache is None else call.cache
             cache = batch.cache_view(owner, writable=call.cache is None)
             x, pending = self.blocks[call.block].forward(rt, x, pending, batch, cache)

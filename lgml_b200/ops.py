@@ -537,10 +537,11 @@ def _value_pages(v_pages: torch.Tensor, k_pages: torch.Tensor, who: str):
 def sink_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
                    k_pages: torch.Tensor, v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int,
                    status: torch.Tensor, slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
-                   gate: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
+                   gate: Optional[torch.Tensor] = None, keep_first: int = 0, softcap: float = 0.0) -> torch.Tensor:
     """out[t, h] = sum_j w_j v_j over the request's keys at positions j <= p with p - j < window (all j <= p
     when window is 0) or j < ``keep_first`` (the request's first tokens stay visible beyond the window),
-    w_j = exp(s_j) / (exp(sink_h) + sum exp(s)), s_j = (q . k_j) scale - slope_h (p - j);
+    w_j = exp(s_j) / (exp(sink_h) + sum exp(s)), s_j = cap((q . k_j) scale) - slope_h (p - j), cap(s) = softcap tanh(s / softcap)
+    (``softcap`` 0: s itself);
     then times sigmoid(gate[t, h]) element by element when ``gate`` (float32, pre-sigmoid; may be a
     column slice) is given.  Keys have head size D, values Dv.  The value pages may have fewer heads than the
     key pages (key heads g Hkv / Hv ... share value head g) and may be a column range of wider cells.
@@ -573,10 +574,10 @@ def sink_attention(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch
             raise KernelError(f"sink_attention: gate {tuple(gate.shape)} is not [{n}, {n_heads * dv}]")
     fn = _fn("attention_sink", "lgml_sink_attention", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                                        c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                       c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
+                                                       c_int, c_int, c_float, c_float, c_int, c_int, c_void_p, c_void_p])
     _check("attention_sink", fn(_ptr(q), dtype_code(q.dtype), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1],
                                 _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out),
-                                dtype_code(out.dtype), ldo, n, n_heads, hkv, hv, d, dv, ldv, float(scale), int(window or 0), int(keep_first or 0),
+                                dtype_code(out.dtype), ldo, n, n_heads, hkv, hv, d, dv, ldv, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first or 0),
                                 _ptr(status), _stream()), "sink_attention")
     return out
 
@@ -587,7 +588,7 @@ SINK_TILE_TOKENS = 64      # query tokens per tile of the tensor-core sink atten
 def sink_attention_mma(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
                        v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int, status: torch.Tensor,
                        slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
-                       gate: Optional[torch.Tensor] = None, keep_first: int = 0) -> torch.Tensor:
+                       gate: Optional[torch.Tensor] = None, keep_first: int = 0, softcap: float = 0.0) -> torch.Tensor:
     """``sink_attention`` for prompts and portions on tensor cores: bfloat16, pages of 64, head sizes
     up to 128.  ``tiles`` int32 [n_tiles, 4]: (request row, first token row, tokens <= 64, 0), each
     tile within one request (``StepBatch.attention_tiles(SINK_TILE_TOKENS)``).  ``out`` bfloat16 or float32."""
@@ -619,10 +620,10 @@ def sink_attention_mma(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Te
             raise KernelError(f"sink_attention_mma: gate {tuple(gate.shape)} is not [{n}, {n_heads * dv}]")
     fn = _fn("attention_sink", "lgml_sink_attention_mma", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                                            c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                           c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
+                                                           c_int, c_int, c_float, c_float, c_int, c_int, c_void_p, c_void_p])
     _check("attention_sink", fn(_ptr(q), ldq, _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(block_table), block_table.shape[1], _ptr(k_pages),
                                 _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), 1 if out.dtype == torch.float32 else 0,
-                                ldo, n_heads, hkv, hv, d, dv, ldv, float(scale), int(window or 0), int(keep_first or 0), _ptr(status), _stream()),
+                                ldo, n_heads, hkv, hv, d, dv, ldv, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first or 0), _ptr(status), _stream()),
            "sink_attention_mma")
     return out
 
@@ -638,7 +639,7 @@ def sink_twin_supports(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor
 def sink_attention_twin(q: torch.Tensor, positions: torch.Tensor, tiles: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
                         v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int, status: torch.Tensor,
                         slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None,
-                        gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        gate: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
     """``sink_attention`` for prompts and portions on tcgen05 tensor cores: the two-tile kernel of
     ``prefill_attention_twin`` with the slopes' bias on the scores, the sink in the denominator and
     the gate on the output.  bfloat16, pages of 64, keys and values of one head size (64 or 128).
@@ -671,10 +672,10 @@ def sink_attention_twin(q: torch.Tensor, positions: torch.Tensor, tiles: torch.T
             raise KernelError(f"sink_attention_twin: gate {tuple(gate.shape)} is not [{n}, {n_heads * d}]")
     fn = _fn("attention_prefill_twin", "lgml_sink_attention_twin", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                                                     c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
-                                                                    c_int, c_float, c_int, c_void_p, c_void_p])
+                                                                    c_int, c_float, c_float, c_int, c_void_p, c_void_p])
     _check("attention_prefill_twin", fn(_ptr(q), ldq, _ptr(positions), _ptr(tiles), tiles.shape[0], _ptr(block_table), block_table.shape[1],
                                         _ptr(k_pages), _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), ldo,
-                                        n_heads, hkv, d, float(scale), int(window or 0), _ptr(status), _stream()), "sink_attention_twin")
+                                        n_heads, hkv, d, float(scale), float(softcap or 0.0), int(window or 0), _ptr(status), _stream()), "sink_attention_twin")
     return out
 
 
@@ -691,7 +692,7 @@ def sink_decode_splits(n_tokens: int, n_kv_heads: int, group: int, reach: int) -
 def sink_decode(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
                 v_pages: torch.Tensor, out: torch.Tensor, n_heads: int, scale: float, window: int, status: torch.Tensor, n_splits: int,
                 slopes: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                keep_first: int = 0) -> torch.Tensor:
+                keep_first: int = 0, softcap: float = 0.0) -> torch.Tensor:
     """``sink_attention`` for decoding and short portions (bfloat16, pages of 64): each token's keys cut into
     ``n_splits`` ranges, the query heads of a KV head scored together, the ranges merged by a second kernel.
     ``out`` bfloat16 or float32."""
@@ -724,10 +725,10 @@ def sink_decode(q: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Te
     scratch = torch.empty(n * n_heads * n_splits * (dv + 2), dtype=torch.float32, device=q.device) if n_splits > 1 else None
     fn = _fn("attention_sink", "lgml_sink_decode", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                                     c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                    c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p])
+                                                    c_int, c_int, c_float, c_float, c_int, c_int, c_void_p, c_void_p])
     _check("attention_sink", fn(_ptr(q), ldq, _ptr(positions), _ptr(seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(k_pages),
                                 _ptr(v_pages), n_pages, page, _ptr(slopes), _ptr(sinks), _ptr(gate), ldg, _ptr(out), 1 if out.dtype == torch.float32 else 0,
-                                ldo, _ptr(scratch), int(n_splits), n, n_heads, hkv, hv, d, dv, ldv, float(scale), int(window or 0), int(keep_first or 0),
+                                ldo, _ptr(scratch), int(n_splits), n, n_heads, hkv, hv, d, dv, ldv, float(scale), float(softcap or 0.0), int(window or 0), int(keep_first or 0),
                                 _ptr(status), _stream()), "sink_decode")
     return out
 
@@ -1137,6 +1138,207 @@ def side_add(x: torch.Tensor, y: torch.Tensor, norm_w: torch.Tensor, eps: float,
 
 # ----------------------------------------------------------------------------------------
 # the gated delta rule
+
+# ----------------------------------------------------------------------------------------
+# layers that norm what they read and what they add; short convolutions; state-space recurrence
+# ----------------------------------------------------------------------------------------
+
+def sandwich_norm(x: torch.Tensor, w_pre: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor], delta=None,
+                  w_post: Optional[torch.Tensor] = None, units=None, row_add: Optional[torch.Tensor] = None,
+                  rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """One kernel over the rows of the float32 residual stream x [tokens, E]:
+
+        m   = delta                                               (a float32 tensor), or
+        m   = 1/2 (a / rms(a) u_a + b / rms(b) u_b)                 (``delta`` = (a, b), ``units`` = (u_a, u_b))
+        x  += LN(m) w_post (+ row_add)                            (``w_post`` None: m is added as it is)
+        out = LN(x) w_pre                                         (``w_pre`` None: no output)
+
+    with LN(v) = (v - mean) / sqrt(var + eps), var the mean of the squared deviations.  With ``rows`` (int32 on the
+    device) only those rows are normed and x is not written."""
+    _need(x, "residual stream", torch.float32, 2)
+    n, E = x.shape
+    if not x.is_contiguous():
+        raise KernelError("sandwich_norm: the residual stream must be contiguous")
+    d1 = d2 = u1 = u2 = None
+    if isinstance(delta, (tuple, list)):
+        d1, d2 = delta
+        u1, u2 = units
+    elif delta is not None:
+        d1 = delta
+    for t, what in ((d1, "delta"), (d2, "second delta")):
+        if t is not None:
+            _need(t, what, torch.float32, 2)
+            if tuple(t.shape) != (n, E) or not t.is_contiguous():
+                raise KernelError(f"sandwich_norm: the {what} must be a contiguous float32 [{n}, {E}], not {tuple(t.shape)}")
+    for t, what in ((u1, "unit weight"), (u2, "second unit weight"), (w_post, "weight of the norm on the delta"), (row_add, "added row"),
+                    (w_pre, "norm weight")):
+        if t is not None:
+            _need(t, what, torch.float32, 1)
+            if t.numel() != E or not t.is_contiguous():
+                raise KernelError(f"sandwich_norm: the {what} must hold {E} floats")
+    n_out = n
+    if rows is not None:
+        _need(rows, "rows", torch.int32, 1)
+        n_out = rows.numel()
+    if w_pre is not None:
+        _need(out, "norm output", ndim=2)
+        if tuple(out.shape) != (n_out, E) or not out.is_contiguous():
+            raise KernelError(f"sandwich_norm: output {tuple(out.shape)} is not a contiguous [{n_out}, {E}]")
+    fn = _fn("norm_conv", "lgml_sandwich_norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                 c_int, c_int, c_int, c_float, c_void_p])
+    _check("norm_conv", fn(_ptr(x), _ptr(d1), _ptr(d2), _ptr(u1), _ptr(u2), _ptr(w_post), _ptr(row_add), _ptr(w_pre), _ptr(rows),
+                           _ptr(out if w_pre is not None else None), dtype_code(out.dtype) if w_pre is not None else F32, n_out, E, float(eps),
+                           _stream()), "sandwich_norm")
+    return out if w_pre is not None else None
+
+
+CONV_MAX_TAPS = 8
+
+
+def short_conv(u: torch.Tensor, w_t: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor], seq_of_token: torch.Tensor,
+               seq_start: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, act: str = "none", residual: bool = False) -> torch.Tensor:
+    """A causal convolution over time on each channel, within each request:
+
+        out[t, c] = [u[t, c] +] act(bias[c] + sum_j w_t[j, c] * u[t - taps + 1 + j, c])
+
+    u float32 [tokens, C] (may be a column slice); ``w_t`` float32 [taps, C], its last row weighs the current token.
+    Inputs before a request's first token of this step come from ``state[slot]`` (float32 [slots, >= (taps - 1) C],
+    the oldest first; zeros for a new request), which then takes the request's last taps - 1 inputs.
+    ``act``: "none" or "silu"; ``residual``: the input is added to the result."""
+    _need(u, "convolution input", torch.float32, 2)
+    _need(w_t, "convolution weights", torch.float32, 2)
+    _need(out, "convolution output", ndim=2)
+    n, C = u.shape
+    taps = w_t.shape[0]
+    ld_in, ld_out = _rows_contiguous(u, "convolution input"), _rows_contiguous(out, "convolution output")
+    if w_t.shape[1] != C or not w_t.is_contiguous() or tuple(out.shape) != (n, C):
+        raise KernelError(f"short_conv: shapes disagree: u {tuple(u.shape)}, weights {tuple(w_t.shape)}, out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, "convolution bias", torch.float32, 1)
+        if bias.numel() != C:
+            raise KernelError("short_conv: one bias per channel")
+    if act not in ("none", "silu"):
+        raise KernelError(f"short_conv: unknown activation '{act}'")
+    ld_state = _state_rows(state, (taps - 1) * C, "short_conv") if taps > 1 else 0
+    fn = _fn("norm_conv", "lgml_short_conv", [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                              c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check("norm_conv", fn(_ptr(u), ld_in, _ptr(w_t), _ptr(bias), _ptr(state if taps > 1 else None), ld_state, _ptr(seq_of_token), _ptr(seq_start),
+                           _ptr(slots), _ptr(out), dtype_code(out.dtype), ld_out, n, C, taps, 1 if act == "silu" else 0, 1 if residual else 0,
+                           _stream()), "short_conv")
+    return out
+
+
+def poly_norm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> torch.Tensor:
+    """out = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e per row, powers element by element, rms(v) =
+    sqrt(mean(v^2) + eps); ``coef`` float32 [4] = (a, b, c, e); z float32 [tokens, F]."""
+    _need(z, "activation input", torch.float32, 2)
+    _need(coef, "activation coefficients", torch.float32, 1)
+    _need(out, "activation output", ndim=2)
+    if coef.numel() != 4 or tuple(out.shape) != tuple(z.shape):
+        raise KernelError(f"poly_norm: four coefficients and an output of the input's shape, not {tuple(coef.shape)} and {tuple(out.shape)}")
+    ldz, ldo = _rows_contiguous(z, "activation input"), _rows_contiguous(out, "activation output")
+    fn = _fn("norm_conv", "lgml_poly_norm", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check("norm_conv", fn(_ptr(z), ldz, _ptr(coef), _ptr(out), dtype_code(out.dtype), ldo, z.shape[0], z.shape[1], float(eps), _stream()), "poly_norm")
+    return out
+
+
+def conv_rope_store(proj: torch.Tensor, w_t: torch.Tensor, state: Optional[torch.Tensor], positions: torch.Tensor, seq_of_token: torch.Tensor,
+                    seq_start: torch.Tensor, slots: torch.Tensor, block_table: torch.Tensor, inv_freq: torch.Tensor, mag: float, n_rot: int,
+                    k_pages: torch.Tensor, v_pages: torch.Tensor, n_heads: int, status: torch.Tensor, write_kv: bool = True) -> torch.Tensor:
+    """From the projection's float32 output ``proj`` [tokens, q (H D) | k (G D) | ...]: q and k through a short causal
+    convolution per channel (``w_t`` float32 [taps, (H + G) D], the last row weighs the current token; the last
+    taps - 1 projected rows of a request wait in ``state[slot]``); the values are the convolved keys' first Dv entries,
+    unrotated; q and k turn by their positions in pairs (i, i + n_rot / 2) with the frequencies ``inv_freq`` ([n_rot / 2]
+    float32, or [2, n_rot / 2] with what float32 lost of each) and cos and sin times ``mag``; k and v go to their
+    cells, q (returned, [tokens, H D]) to a buffer of the cache's type."""
+    _need(proj, "projection output", torch.float32, 2)
+    _need(w_t, "convolution weights", torch.float32, 2)
+    _need(k_pages, "key pages", ndim=4)
+    _need(v_pages, "value pages", k_pages.dtype, 4)
+    ldp = _rows_contiguous(proj, "projection output")
+    n = proj.shape[0]
+    n_pages, G, page, D = k_pages.shape
+    Dv = v_pages.shape[3]
+    C = (n_heads + G) * D
+    taps = w_t.shape[0]
+    if tuple(v_pages.shape[:3]) != (n_pages, G, page) or not k_pages.is_contiguous() or not v_pages.is_contiguous():
+        raise KernelError(f"conv_rope_store: key pages {tuple(k_pages.shape)} and value pages {tuple(v_pages.shape)} do not go together")
+    if proj.shape[1] < C or w_t.shape[1] != C or not w_t.is_contiguous():
+        raise KernelError(f"conv_rope_store: {proj.shape[1]} columns / weights {tuple(w_t.shape)} do not fit q and k of {C} channels")
+    for t, what in ((positions, "positions"), (seq_of_token, "request index of tokens")):
+        _need(t, what, torch.int32, 1)
+        if t.numel() != n:
+            raise KernelError(f"conv_rope_store: one of the {what} per token")
+    _need(block_table, "block table", torch.int32, 2)
+    if not block_table.is_contiguous():
+        raise KernelError("conv_rope_store: the block table is not contiguous")
+    freq_lo = None
+    if inv_freq.dim() == 2:
+        if inv_freq.shape[0] != 2 or not inv_freq.is_contiguous():
+            raise KernelError("conv_rope_store: frequencies with low parts are a contiguous [2, n_rot / 2]")
+        inv_freq, freq_lo = inv_freq[0], inv_freq[1]
+    _need(inv_freq, "rotary frequencies", torch.float32, 1)
+    if n_rot % 2 or n_rot > D or inv_freq.numel() < max(n_rot // 2, 1):
+        raise KernelError(f"conv_rope_store: n_rot {n_rot} must be even, at most the head size {D}, and have n_rot / 2 frequencies")
+    ld_state = _state_rows(state, (taps - 1) * C, "conv_rope_store") if taps > 1 else 0
+    q_out = torch.empty((n, n_heads * D), dtype=k_pages.dtype, device=proj.device)
+    fn = _fn("rope_cache", "lgml_conv_rope_store", [c_void_p, c_int, c_void_p, c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                    c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int,
+                                                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check("rope_cache", fn(_ptr(proj), ldp, _ptr(w_t), _ptr(state if taps > 1 else None), ld_state, taps, _ptr(q_out), dtype_code(k_pages.dtype),
+                            q_out.stride(0), _ptr(positions), _ptr(seq_of_token), _ptr(seq_start), _ptr(slots), _ptr(block_table), block_table.shape[1],
+                            _ptr(inv_freq), _ptr(freq_lo), float(mag), int(n_rot), _ptr(k_pages), _ptr(v_pages), n_pages, page, n, n_heads, G, D, Dv,
+                            1 if write_kv else 0, _ptr(status), _stream()), "conv_rope_store")
+    return q_out
+
+
+def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor,
+             seq_start: torch.Tensor, slots: torch.Tensor, n_heads: int, n_groups: int, head_dim: int, n_state: int) -> torch.Tensor:
+    """The state-space recurrence of a step's tokens, request by request (all float32):
+
+        dt = softplus(dt_raw + dt_bias_h);  S <- exp(-exp(A_log_h) dt) S + dt B x^T;  y = S^T C + D_h x
+
+    ``xbc`` [tokens, x (Hs P) | B (G N) | C (G N)] and ``dt_raw`` [tokens, Hs] may be column slices; head h reads group
+    h // (Hs / G).  S ([N, P] per head, stored column by column) lives in ``state[slot]`` (float32 [slots, >= Hs P N]).
+    Returns y float32 [tokens, Hs P]."""
+    _need(xbc, "convolved x, B and C", torch.float32, 2)
+    _need(dt_raw, "step sizes", torch.float32, 2)
+    ldx, ldd = _rows_contiguous(xbc, "convolved x, B and C"), _rows_contiguous(dt_raw, "step sizes")
+    n = xbc.shape[0]
+    inner = n_heads * head_dim
+    if xbc.shape[1] != inner + 2 * n_groups * n_state or tuple(dt_raw.shape) != (n, n_heads):
+        raise KernelError(f"ssd_scan: xbc {tuple(xbc.shape)} / dt {tuple(dt_raw.shape)} do not fit {n_heads} heads of {head_dim}, {n_groups} groups of {n_state}")
+    for t, what in ((dt_bias, "step bias"), (a_log, "decay logarithms"), (d_skip, "skip weights")):
+        _need(t, what, torch.float32, 1)
+        if t.numel() != n_heads or not t.is_contiguous():
+            raise KernelError(f"ssd_scan: one of the {what} per head")
+    ld_state = _state_rows(state, inner * n_state, "ssd_scan")
+    y = torch.empty((n, inner), dtype=torch.float32, device=xbc.device)
+    n_seqs = seq_start.numel() - 1
+    fn = _fn("ssd", "lgml_ssd_scan", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check("ssd", fn(_ptr(xbc), ldx, _ptr(dt_raw), ldd, _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), ld_state, _ptr(seq_start), _ptr(slots),
+                     _ptr(y), inner, n_seqs, n_heads, n_groups, head_dim, n_state, _stream()), "ssd_scan")
+    return y
+
+
+def ssd_gate_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, groups: int, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """out = (y silu(z)) over the root mean square of each of ``groups`` equal parts of a row, times ``weight``; y and z
+    float32 [tokens, inner] (z may be a column slice)."""
+    _need(y, "recurrence output", torch.float32, 2)
+    _need(z, "gate", torch.float32, 2)
+    _need(weight, "norm weight", torch.float32, 1)
+    n, inner = y.shape
+    ldy, ldz = _rows_contiguous(y, "recurrence output"), _rows_contiguous(z, "gate")
+    if tuple(z.shape) != (n, inner) or weight.numel() != inner or inner % groups:
+        raise KernelError(f"ssd_gate_norm: y {tuple(y.shape)}, z {tuple(z.shape)}, weight {tuple(weight.shape)}, {groups} parts do not fit")
+    out = torch.empty((n, inner), dtype=out_dtype, device=y.device)
+    fn = _fn("ssd", "lgml_ssd_gate_norm", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check("ssd", fn(_ptr(y), ldy, _ptr(z), ldz, _ptr(weight), _ptr(out), dtype_code(out_dtype), inner, n, inner, int(groups), float(eps), _stream()),
+           "ssd_gate_norm")
+    return out
+
+
 # ----------------------------------------------------------------------------------------
 
 def delta_prepare(proj: torch.Tensor, a_pre: torch.Tensor, conv_w: torch.Tensor, state: torch.Tensor, conv_off: int,

@@ -19,9 +19,12 @@ from __future__ import annotations
 
 import dataclasses
 
+import torch
+
 from .. import ops
 from ..cache import FixedState
 from .base import Part, register_part
+from .norm import PendingDelta
 
 
 class PreNormBlock(Part):
@@ -96,4 +99,88 @@ class PreNormBlock(Part):
         return x, pending
 
 
+class SandwichBlock(Part):
+    """A layer that norms what a sublayer reads and what it adds:
+
+        x = x + post1(mixer(conv1(pre1(x))));   x = x + post2(ffn(conv2(pre2(x))))
+
+    ``conv1`` / ``conv2`` (``parts/token_mix.py``: ``InputConv``) are optional.  A sum, the norm on what is added and the
+    next norm on x are one kernel: the block hands its last result on as a ``PendingDelta`` with the weight of
+    the norm it still has to pass, and the next norm (the next block's, or the model's final one, which must
+    take such a delta) does both.  The layer's fixed state is one row per request: the convolutions' rows first,
+    the mixer's own state behind them."""
+
+    takes_pending_row = True
+
+    def __init__(self, mixer_norm, mixer_post, mixer, ffn_norm, ffn_post, ffn, mixer_conv=None, ffn_conv=None, names=None):
+        self.mixer_norm, self.mixer_post, self.mixer = mixer_norm, mixer_post, mixer
+        self.ffn_norm, self.ffn_post, self.ffn = ffn_norm, ffn_post, ffn
+        self.mixer_conv, self.ffn_conv = mixer_conv, ffn_conv
+        self.names = {"mixer_norm": "norm1", "mixer_post": "norm1b", "mixer": "mix", "ffn_norm": "norm2", "ffn_post": "norm2b", "ffn": "mlp",
+                      "mixer_conv": "canon1", "ffn_conv": "canon2"}
+        self.names.update(names or {})
+        if ffn is None and (ffn_norm is not None or ffn_post is not None or ffn_conv is not None):
+            raise ValueError("a layer without a feed-forward has no norms or convolution for it")
+        paged, own = None, 0
+        spec = mixer.cache_spec()
+        for sp in (spec if isinstance(spec, (tuple, list)) else (spec,)):
+            if isinstance(sp, FixedState):
+                if len(sp.shape) != 1 or sp.dtype != torch.float32:
+                    raise TypeError(f"the layer's state slot holds rows of float32 only, not {sp}")
+                own = sp.shape[0]
+            elif sp is not None:
+                paged = sp
+        conv_floats = [c.cache_spec().shape[0] if c is not None and c.cache_spec() is not None else 0 for c in (mixer_conv, ffn_conv)]
+        self._paged, self._floats = paged, (conv_floats[0], conv_floats[1], own)
+
+    def _parts(self, prefix):
+        for key in ("mixer_norm", "mixer_post", "mixer_conv", "mixer", "ffn_norm", "ffn_post", "ffn_conv", "ffn"):
+            part = getattr(self, key)
+            if part is not None:
+                yield part, f"{prefix}.{self.names[key]}"
+
+    def tensor_specs(self, prefix):
+        return [s for part, p in self._parts(prefix) for s in part.tensor_specs(p)]
+
+    def bind(self, prefix, tensors, rt):
+        for part, p in self._parts(prefix):
+            part.bind(p, tensors, rt)
+
+    def cache_spec(self):
+        total = sum(self._floats)
+        both = tuple(s for s in (self._paged, FixedState((total,), torch.float32) if total else None) if s is not None)
+        return both if len(both) > 1 else (both[0] if both else None)
+
+    @property
+    def graph_safe(self):
+        return all(getattr(part, "graph_safe", False) for part, _ in self._parts(""))
+
+    @staticmethod
+    def _pend(delta, post):
+        return PendingDelta(delta, post.weight, eps=post.eps) if post is not None else PendingDelta(delta)
+
+    def forward(self, rt, x, pending, batch, cache):
+        c1, c2, own = self._floats
+        state = cache.state
+
+        def read(norm, conv, first, floats, pend):
+            if conv is None:
+                return norm.forward(rt, x, rt.dtype, delta=pend)
+            h = norm.forward(rt, x, conv.input_dtype, delta=pend)
+            return conv.forward(rt, h, batch, state[:, first:first + floats] if floats else None)
+
+        h = read(self.mixer_norm, self.mixer_conv, 0, c1, pending)
+        if self.ffn is not None:
+            first = getattr(self.ffn, "first_weights", None)
+            if first is not None:
+                rt.ahead(first())
+        mixer_cache = dataclasses.replace(cache, state=state[:, c1 + c2:c1 + c2 + own] if own else None)
+        pending = self._pend(self.mixer.forward(rt, h, batch, mixer_cache), self.mixer_post)
+        if self.ffn is not None:
+            h = read(self.ffn_norm, self.ffn_conv, c1, c2, pending)
+            pending = self._pend(self.ffn.forward(rt, h), self.ffn_post)
+        return x, pending
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "sandwich", SandwichBlock)

@@ -135,6 +135,36 @@ class ClampedGLU(Part):
         return rt.linear(act, self.wd, partials_ok=True)
 
 
+class PolyNormMLP(Part):
+    """down(act(up(h))) with act(z) = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e: powers element by
+    element, every power over its own root mean square along the row (eps inside the root); the four numbers
+    are the tensor ``.act``.  The first product's result and the activation are float32."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, inner: int, eps: float, names=(".up", ".down", ".act")):
+        self.width, self.inner, self.eps, self.names = width, inner, float(eps), tuple(names)
+        self.wu = self.wd = self.coef = None
+
+    def tensor_specs(self, prefix):
+        return [TensorSpec(prefix + self.names[0], (self.inner, self.width)), TensorSpec(prefix + self.names[1], (self.width, self.inner)),
+                TensorSpec(prefix + self.names[2], (4,), VECTOR, init=(0.5, 5.0))]
+
+    def bind(self, prefix, tensors, rt):
+        self.wu, self.wd = tensors[prefix + self.names[0]], tensors[prefix + self.names[1]]
+        self.coef = tensors[prefix + self.names[2]].float().contiguous()
+
+    def first_weights(self):
+        return [self.wu]
+
+    def forward(self, rt, h):
+        z = rt.linear(h, self.wu, out_dtype=torch.float32)
+        act = torch.empty(z.shape, dtype=rt.dtype, device=z.device)
+        ops.poly_norm(z, self.coef, self.eps, act)
+        return rt.linear(act, self.wd, out_dtype=torch.float32)
+
+
 register_part("feed_forward", "gated_mlp", GatedMLP)
 register_part("feed_forward", "clamped_glu", ClampedGLU)
 register_part("feed_forward", "dense_mlp", DenseMLP)
+register_part("feed_forward", "polynorm_mlp", PolyNormMLP)

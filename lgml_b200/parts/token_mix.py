@@ -79,5 +79,38 @@ class TokenSide(Part):
         return ops.side_add(x, y, self.norm_w, self.eps, scale)
 
 
+class InputConv(Part):
+    """What a sublayer reads gains a causal convolution of itself over time, per channel:
+
+        y_t = h_t + sum_j w[:, j] * h_(t - taps + 1 + j)        zeros before a request's start
+
+    The tensor is [width, taps]; its last column weighs the current row.  The last taps - 1 rows of h wait,
+    float32, in the request's state slot.  Takes float32 rows (the norm before it writes them so) and gives
+    rows in the compute type."""
+
+    graph_safe = True
+    input_dtype = torch.float32
+
+    def __init__(self, width: int, taps: int):
+        if not 1 <= taps <= ops.CONV_MAX_TAPS:
+            raise ValueError(f"a convolution of {taps} taps (1 to {ops.CONV_MAX_TAPS})")
+        self.width, self.taps = width, int(taps)
+        self.w_t = None
+
+    def cache_spec(self):
+        return FixedState(((self.taps - 1) * self.width,), torch.float32) if self.taps > 1 else None
+
+    def tensor_specs(self, prefix):
+        return [TensorSpec(prefix, (self.width, self.taps), VECTOR, init=(0.0, 10.0))]
+
+    def bind(self, prefix, tensors, rt):
+        self.w_t = tensors[prefix].float().t().contiguous()
+
+    def forward(self, rt, h, batch, state):
+        out = torch.empty(h.shape, dtype=rt.dtype, device=h.device)
+        return ops.short_conv(h, self.w_t, None, state, batch.seq_of_token, batch.seq_start, batch.slots, out, residual=True)
+
+
 register_part("token_input", "token_shift", TokenShift)
+register_part("token_input", "input_conv", InputConv)
 register_part("token_input", "token_side", TokenSide)
