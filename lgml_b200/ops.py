@@ -1184,6 +1184,8 @@ def sandwich_norm(x: torch.Tensor, w_pre: Optional[torch.Tensor], eps: float, ou
         _need(out, "norm output", ndim=2)
         if tuple(out.shape) != (n_out, E) or not out.is_contiguous():
             raise KernelError(f"sandwich_norm: output {tuple(out.shape)} is not a contiguous [{n_out}, {E}]")
+    if n_out == 0:
+        return out if w_pre is not None else None
     fn = _fn("norm_conv", "lgml_sandwich_norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                  c_int, c_int, c_int, c_float, c_void_p])
     _check("norm_conv", fn(_ptr(x), _ptr(d1), _ptr(d2), _ptr(u1), _ptr(u2), _ptr(w_post), _ptr(row_add), _ptr(w_pre), _ptr(rows),
