@@ -1,7 +1,7 @@
 """Configuration of the Dizepel decoder, from its own ``config.json`` keys.
 
 ``architecture`` names it; ``vocab``, ``width``, ``norm.eps``, ``embedding.scale`` (the factor on the embedding's
-rows; absent: 1) and ``canon.taps`` (the taps of the convolution on what every sublayer reads; absent or 1: none)
+rows; absent: 1) and ``canon.taps`` (the taps of the convolution on what every sublayer reads; absent: none)
 are the model's own numbers.  ``layers`` lists the layers one by one: ``type`` (the mixer: ``parallel``), ``mixer``
 (its sizes and constants) and ``mlp`` (the feed-forward, or null for a layer without one).  ``loop`` (``start``,
 ``stop``, ``times``): layers start .. stop - 1 run ``times`` times in a row with the same weights; every pass adds
@@ -34,7 +34,7 @@ class DizepelConfig(ModelConfig):
     width: int = 0
     norm_eps: float = 0.0
     embed_scale: float = 1.0
-    canon_taps: int = 1
+    canon_taps: int = 0                    # 0: no convolution on what the sublayers read
     loop: Optional[Tuple[int, int, int]] = None      # (start, stop, times)
     layers: List[Dict[str, Any]] = field(default_factory=list)
     torch_dtype: str = "bfloat16"
@@ -89,7 +89,7 @@ class DizepelConfig(ModelConfig):
             loop = (loop["start"], loop["stop"], loop["times"])
         return cls(vocab=int(d["vocab"]), width=int(d["width"]), norm_eps=float(norm["eps"]),
                    embed_scale=float(_number("embedding", emb, "scale")) if emb and "scale" in emb else 1.0,
-                   canon_taps=_positive_int("canon", canon, "taps") if canon and "taps" in canon else 1,
+                   canon_taps=_positive_int("canon", canon, "taps") if canon is not None else 0,
                    loop=loop, layers=copy.deepcopy(d["layers"]), torch_dtype=str(d.get("torch_dtype", "bfloat16")))
 
     def validate(self) -> None:
@@ -99,7 +99,7 @@ class DizepelConfig(ModelConfig):
             raise ConfigError("config.json: norm.eps must be positive")
         if not self.layers:
             raise ConfigError("config.json: 'layers' is empty")
-        if not 1 <= self.canon_taps <= 8:
+        if not 0 <= self.canon_taps <= 8:
             raise ConfigError(f"config.json: canon.taps must be 1 to 8, not {self.canon_taps}")
         if self.loop is not None:
             a, b, times = self.loop
@@ -156,7 +156,9 @@ class DizepelConfig(ModelConfig):
 
     def to_dict(self) -> Dict[str, Any]:
         d = {"architecture": self.architecture, "vocab": self.vocab, "width": self.width, "norm": {"eps": self.norm_eps},
-             "embedding": {"scale": self.embed_scale}, "canon": {"taps": self.canon_taps}, "layers": copy.deepcopy(self.layers)}
+             "embedding": {"scale": self.embed_scale}, "layers": copy.deepcopy(self.layers)}
+        if self.canon_taps:
+            d["canon"] = {"taps": self.canon_taps}
         if self.loop is not None:
             d["loop"] = {"start": self.loop[0], "stop": self.loop[1], "times": self.loop[2]}
         return d

@@ -43,7 +43,7 @@ def feed_forward_of(cfg: DizepelConfig, mlp):
 
 def build_dizepel(cfg: DizepelConfig) -> DecoderModel:
     norm = lambda: make_part("norm", "layernorm", width=cfg.width, eps=cfg.norm_eps)
-    conv = lambda: make_part("token_input", "input_conv", width=cfg.width, taps=cfg.canon_taps) if cfg.canon_taps > 1 else None
+    conv = lambda: make_part("token_input", "input_conv", width=cfg.width, taps=cfg.canon_taps) if cfg.canon_taps else None
     blocks = []
     for layer in cfg.layers:
         ffn = feed_forward_of(cfg, layer.get("mlp"))
@@ -54,8 +54,7 @@ def build_dizepel(cfg: DizepelConfig) -> DecoderModel:
     embedding = TokenEmbedding(cfg.vocab, cfg.width, name="embed")
     head = LMHead(cfg.vocab, cfg.width, name="head")
     return DecoderModel(cfg, embedding, blocks, norm(), head, schedule=schedule, block_prefix="l{}", final_norm_prefix="final.norm",
-                        embed_scale=cfg.embed_scale if cfg.embed_scale != 1.0 else None, delta_dtype=torch.float32, pass_rows="loop.step",
-                        ignored_tensors=("l*.canon*",) if cfg.canon_taps <= 1 else ())
+                        embed_scale=cfg.embed_scale if cfg.embed_scale != 1.0 else None, delta_dtype=torch.float32, pass_rows="loop.step")
 
 
 register_architecture("Dizepel", DizepelConfig, build_dizepel)

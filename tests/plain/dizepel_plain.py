@@ -188,14 +188,17 @@ def layer_runs(cfg):
     return runs + [(i, None) for i in range(b, n)]
 
 
-def layer(x, W, i, spec, eps):
+def layer(x, W, i, spec, eps, input_conv=True):
+    """One layer; ``input_conv``: what each sublayer reads gains a causal convolution of itself."""
     p = f"l{i}"
     h = layer_norm(x, W[p + ".norm1"], eps)
-    h = h + causal_conv(h, W[p + ".canon1"])
+    if input_conv:
+        h = h + causal_conv(h, W[p + ".canon1"])
     x = x + layer_norm(parallel_mixer(h, W, p + ".mix", spec["mixer"], eps), W[p + ".norm1b"], eps)
     if spec.get("mlp") is not None:
         h = layer_norm(x, W[p + ".norm2"], eps)
-        h = h + causal_conv(h, W[p + ".canon2"])
+        if input_conv:
+            h = h + causal_conv(h, W[p + ".canon2"])
         x = x + layer_norm(feed_forward(h, W, p + ".mlp", eps), W[p + ".norm2b"], eps)
     return x
 
@@ -207,7 +210,7 @@ def forward(cfg, W, tokens, trace=None):
     for i, t in layer_runs(cfg):
         if t is not None:
             x = x + W["loop.step"][t]
-        x = layer(x, W, i, cfg["layers"][i], eps)
+        x = layer(x, W, i, cfg["layers"][i], eps, input_conv=cfg.get("canon") is not None)
         if trace is not None:
             trace.append(x.copy())
     return layer_norm(x, W["final.norm"], eps) @ W["head"].T
