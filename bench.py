@@ -16,7 +16,7 @@ measured copy bandwidth, and ``roofline_points`` the same fraction for every bat
 
 ``--shape llama32_3b`` runs that shape's own workload (32 prompts of 128 to 4,096 tokens in
 portions of 512 beside decodes, 512 new tokens each) through ``Engine.generate``;
-``--shape llama2_13b`` decodes at batch 16 after 3,584-token prompts; ``--design lefulorn`` (or ``gotulorn``, ``konovik``)
+``--shape llama2_13b`` decodes at batch 16 after 3,584-token prompts; ``--design lefulorn`` (or ``gotulorn``, ``konovik``, ``dizepel``)
 times that design beside the Llama decoder at equal layer sizes; ``--cpu-baseline`` times the
 plain CPU implementation at the tiny configurations.
 """
@@ -339,7 +339,21 @@ def konovik_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int,
             "layers": out}
 
 
-DESIGN_SHAPES = {"lefulorn": lefulorn_shape, "gotulorn": gotulorn_shape, "konovik": konovik_shape}
+def dizepel_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, layers: int, window: int, vocab: int) -> dict:
+    """Dizepel with layers of a real model's size: every layer the parallel mixer (attention whose values are its keys:
+    heads of ``head_dim`` of which half turn, stretched frequencies, four taps on q and k, a cap of 30 and a sink; beside
+    it a state-space recurrence as wide as the model: heads of 64, a state of 128 numbers, one group, four taps) and the
+    dense feed-forward of the full inner width (as many weights as the gated one of two thirds of it); four taps on what
+    the sublayers read; no loop (the Llama decoder beside it runs every layer once)."""
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "conv": 4, "scale": head_dim ** -0.5, "softcap": 30.0,
+            "rot": {"base": 250000.0, "dims": head_dim // 2, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    right = {"heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    layer = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Dizepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "canon": {"taps": 4},
+            "layers": [dict(layer) for _ in range(layers)]}
+
+
+DESIGN_SHAPES = {"lefulorn": lefulorn_shape, "gotulorn": gotulorn_shape, "konovik": konovik_shape, "dizepel": dizepel_shape}
 
 DESIGN_SIZES = {          # name -> width, heads, KV heads, head size, dense inner width, layers
     "w2048": (2048, 16, 4, 128, 8192, 4),
@@ -458,7 +472,7 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=0, help="context (tokens a request may hold) instead of the shape's own")
     ap.add_argument("--prefill-tokens", type=int, default=0, help="tokens of the timed prompt instead of 2,048 (read in portions of 2,048)")
     ap.add_argument("--no-kernel-times", action="store_true", help="leave out the per-kernel-class times of a decode step")
-    ap.add_argument("--design", default="", choices=["", "lefulorn", "gotulorn", "konovik"], help="time this design beside the Llama decoder at equal layer sizes "
+    ap.add_argument("--design", default="", choices=["", "lefulorn", "gotulorn", "konovik", "dizepel"], help="time this design beside the Llama decoder at equal layer sizes "
                     "(prefill and decode, with kernel-class times) instead of the headline workload")
     ap.add_argument("--cpu-baseline", action="store_true", help="time the plain CPU implementation at the tiny configurations and stop")
     args = ap.parse_args()

@@ -33,6 +33,13 @@ struct SandwichArgs {
     void *out;                      // [n_out, E]
     int E;
     float eps;
+    // a step of one token a request: the convolution of the normed rows over time in the same kernel
+    // (out = h + sum_j conv_w[j] h_(t - taps + 1 + j), the request's last taps - 1 rows of h in its slot)
+    const float *conv_w;            // [taps, E] or null
+    float *conv_state;
+    long long conv_state_ld;
+    const int *slots;
+    int taps;
 };
 
 // sum over the block of two numbers at once, fixed order
@@ -48,12 +55,12 @@ __device__ __forceinline__ float2 block_sum2(float a, float b, float2 *red) {
 }
 
 template <typename TO>
-__global__ void __launch_bounds__(ROW_THREADS) sandwich_norm_kernel(const SandwichArgs a) {
+__global__ void __launch_bounds__(1024) sandwich_norm_kernel(const SandwichArgs a) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float row[];          // E floats: m, then x
     __shared__ float2 red[32];
-    const int E = a.E, tid = threadIdx.x;
+    const int E = a.E, tid = threadIdx.x, nthr = blockDim.x;
     const int r = blockIdx.x;
     const size_t src = a.rows ? (size_t)a.rows[r] : (size_t)r;
     float *xr = a.x + src * E;
@@ -64,30 +71,30 @@ __global__ void __launch_bounds__(ROW_THREADS) sandwich_norm_kernel(const Sandwi
         if (a.d2 != nullptr) {
             const float *d2 = a.d2 + src * E;
             float s1 = 0.f, s2 = 0.f;
-            for (int i = tid; i < E; i += ROW_THREADS) {
+            for (int i = tid; i < E; i += nthr) {
                 const float p = act_load(d1 + i), q = act_load(d2 + i);
                 s1 = fmaf(p, p, s1), s2 = fmaf(q, q, s2);
             }
             const float2 ss = block_sum2(s1, s2, red);
             const float i1 = 0.5f / sqrtf(ss.x * invE + a.eps), i2 = 0.5f / sqrtf(ss.y * invE + a.eps);
-            for (int i = tid; i < E; i += ROW_THREADS)
+            for (int i = tid; i < E; i += nthr)
                 row[i] = act_load(d1 + i) * i1 * __ldg(a.u1 + i) + act_load(d2 + i) * i2 * __ldg(a.u2 + i);
         } else {
-            for (int i = tid; i < E; i += ROW_THREADS) row[i] = act_load(d1 + i);
+            for (int i = tid; i < E; i += nthr) row[i] = act_load(d1 + i);
         }
         float mean = 0.f, inv = 1.f;
         if (a.w_post != nullptr) {
             float s = 0.f;
-            for (int i = tid; i < E; i += ROW_THREADS) s += row[i];
+            for (int i = tid; i < E; i += nthr) s += row[i];
             mean = block_sum2(s, 0.f, red).x * invE;
             float v = 0.f;
-            for (int i = tid; i < E; i += ROW_THREADS) {
+            for (int i = tid; i < E; i += nthr) {
                 const float c = row[i] - mean;
                 v = fmaf(c, c, v);
             }
             inv = 1.0f / sqrtf(block_sum2(v, 0.f, red).x * invE + a.eps);
         }
-        for (int i = tid; i < E; i += ROW_THREADS) {
+        for (int i = tid; i < E; i += nthr) {
             float m = row[i];
             if (a.w_post != nullptr) m = (m - mean) * inv * __ldg(a.w_post + i);
             float xv = act_load(xr + i) + m;
@@ -96,7 +103,7 @@ __global__ void __launch_bounds__(ROW_THREADS) sandwich_norm_kernel(const Sandwi
             if (a.rows == nullptr) xr[i] = xv;
         }
     } else {
-        for (int i = tid; i < E; i += ROW_THREADS) {
+        for (int i = tid; i < E; i += nthr) {
             float xv = act_load(xr + i);
             if (a.row_add != nullptr) {
                 xv += __ldg(a.row_add + i);
@@ -107,16 +114,34 @@ __global__ void __launch_bounds__(ROW_THREADS) sandwich_norm_kernel(const Sandwi
     }
     if (a.w_pre == nullptr) return;
     float s = 0.f;
-    for (int i = tid; i < E; i += ROW_THREADS) s += row[i];
+    for (int i = tid; i < E; i += nthr) s += row[i];
     const float mean = block_sum2(s, 0.f, red).x * invE;
     float v = 0.f;
-    for (int i = tid; i < E; i += ROW_THREADS) {
+    for (int i = tid; i < E; i += nthr) {
         const float c = row[i] - mean;
         v = fmaf(c, c, v);
     }
     const float inv = 1.0f / sqrtf(block_sum2(v, 0.f, red).x * invE + a.eps);
     TO *orow = reinterpret_cast<TO *>(a.out) + (size_t)r * E;
-    for (int i = tid; i < E; i += ROW_THREADS) orow[i] = from_f32<TO>((row[i] - mean) * inv * __ldg(a.w_pre + i));
+    if (a.conv_w == nullptr) {
+        for (int i = tid; i < E; i += nthr) orow[i] = from_f32<TO>((row[i] - mean) * inv * __ldg(a.w_pre + i));
+        return;
+    }
+    // row r is the one token of request r: the same sums in the same order as short_conv's
+    const int back = a.taps - 1;
+    float *st = a.conv_state + (size_t)a.slots[r] * a.conv_state_ld;
+    for (int i = tid; i < E; i += nthr) {
+        const float h = (row[i] - mean) * inv * __ldg(a.w_pre + i);
+        float acc = 0.f, old[MAX_TAPS];
+        for (int j = 0; j < back; ++j) old[j] = act_load(st + (size_t)j * E + i);       // every load before the first store
+        for (int j = 0; j < back; ++j) {
+            acc = fmaf(__ldg(a.conv_w + (size_t)j * E + i), old[j], acc);
+            if (j > 0) st[(size_t)(j - 1) * E + i] = old[j];
+        }
+        if (back > 0) st[(size_t)(back - 1) * E + i] = h;
+        acc = fmaf(__ldg(a.conv_w + (size_t)back * E + i), h, acc);
+        orow[i] = from_f32<TO>(acc + h);
+    }
 }
 
 __device__ __forceinline__ float silu_(float v) { return v / (1.0f + expf(-v)); }
@@ -183,14 +208,14 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const float *__restrict
 
 // z float32 [n, F] -> out [n, F]; coef float32 [4] = a, b, c, e
 template <typename TO>
-__global__ void __launch_bounds__(ROW_THREADS) poly_norm_kernel(const float *__restrict__ z, int ldz, const float *__restrict__ coef,
+__global__ void __launch_bounds__(1024) poly_norm_kernel(const float *__restrict__ z, int ldz, const float *__restrict__ coef,
                                                                 TO *__restrict__ out, int ldo, int F, float eps) {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[32];
     const float *zr = z + (size_t)blockIdx.x * ldz;
     float s1 = 0.f, s2 = 0.f, s3 = 0.f;
-    for (int i = threadIdx.x; i < F; i += ROW_THREADS) {
+    for (int i = threadIdx.x; i < F; i += blockDim.x) {
         const float v = act_load(zr + i), v2 = v * v;
         s1 += v2, s2 = fmaf(v2, v2, s2), s3 = fmaf(v2 * v2, v2, s3);
     }
@@ -199,7 +224,7 @@ __global__ void __launch_bounds__(ROW_THREADS) poly_norm_kernel(const float *__r
     const float a = __ldg(coef) / sqrtf(s1 * invF + eps), b = __ldg(coef + 1) / sqrtf(s2 * invF + eps),
                 c = __ldg(coef + 2) / sqrtf(s3 * invF + eps), e = __ldg(coef + 3);
     TO *orow = out + (size_t)blockIdx.x * ldo;
-    for (int i = threadIdx.x; i < F; i += ROW_THREADS) {
+    for (int i = threadIdx.x; i < F; i += blockDim.x) {
         const float v = act_load(zr + i);
         orow[i] = from_f32<TO>(fmaf(v, fmaf(v, fmaf(v, c, b), a), e));
     }
@@ -214,20 +239,25 @@ static inline int grid_for(size_t items, int block) {
 
 LGML_API int lgml_sandwich_norm(float *x, const float *d1, const float *d2, const float *u1, const float *u2, const float *w_post,
                                 const float *row_add, const float *w_pre, const int *rows, void *out, int out_dtype, int n_out, int E, float eps,
-                                cudaStream_t stream) {
+                                const float *conv_w, float *conv_state, long long conv_state_ld, const int *slots, int taps, cudaStream_t stream) {
     LGML_REQUIRE(n_out >= 0 && E > 0, "sandwich_norm: bad sizes");
     LGML_REQUIRE(d2 == nullptr || (d1 != nullptr && u1 != nullptr && u2 != nullptr), "sandwich_norm: two deltas come with their unit weights");
     LGML_REQUIRE(w_pre == nullptr || out != nullptr, "sandwich_norm: a norm needs its output");
     LGML_REQUIRE((size_t)E * sizeof(float) <= 200 * 1024, "sandwich_norm: rows of %d floats do not fit shared memory", E);
+    LGML_REQUIRE(conv_w == nullptr || (w_pre != nullptr && rows == nullptr && slots != nullptr && taps >= 1 && taps <= MAX_TAPS &&
+                                       (taps == 1 || (conv_state != nullptr && conv_state_ld >= (long long)(taps - 1) * E))),
+                 "sandwich_norm: the convolution in the same kernel needs a norm, all rows, the slots and a state of taps - 1 rows");
     if (n_out == 0) return 0;
-    SandwichArgs a{x, d1, d2, u1, u2, w_post, row_add, w_pre, rows, out, E, eps};
+    SandwichArgs a{x, d1, d2, u1, u2, w_post, row_add, w_pre, rows, out, E, eps, conv_w, conv_state, conv_state_ld, slots, taps};
     const size_t smem = (size_t)E * sizeof(float);
+    // few rows (a decode step): a row's passes are latency, so more threads share it; many rows: blocks of 256 fill the SMs
+    const int threads = (n_out <= 296 && E >= 1024) ? 1024 : ROW_THREADS;
     if (out_dtype == LGML_F32) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(sandwich_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lgml_launch(sandwich_norm_kernel<float>, n_out, ROW_THREADS, smem, stream, a);
+        lgml_launch(sandwich_norm_kernel<float>, n_out, threads, smem, stream, a);
     } else if (out_dtype == LGML_BF16) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(sandwich_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lgml_launch(sandwich_norm_kernel<__nv_bfloat16>, n_out, ROW_THREADS, smem, stream, a);
+        lgml_launch(sandwich_norm_kernel<__nv_bfloat16>, n_out, threads, smem, stream, a);
     } else {
         LGML_FAIL("sandwich_norm: unknown output type %d", out_dtype);
     }
@@ -255,9 +285,10 @@ LGML_API int lgml_poly_norm(const float *z, int ldz, const float *coef, void *ou
                             cudaStream_t stream) {
     LGML_REQUIRE(n_tokens >= 0 && F > 0 && ldz >= F && ldo >= F, "poly_norm: bad sizes");
     if (n_tokens == 0) return 0;
-    if (out_dtype == LGML_F32) lgml_launch(poly_norm_kernel<float>, n_tokens, ROW_THREADS, 0, stream, z, ldz, coef, (float *)out, ldo, F, eps);
+    const int threads = (n_tokens <= 296 && F >= 1024) ? 1024 : ROW_THREADS;      // few rows: more threads share a row's latency
+    if (out_dtype == LGML_F32) lgml_launch(poly_norm_kernel<float>, n_tokens, threads, 0, stream, z, ldz, coef, (float *)out, ldo, F, eps);
     else if (out_dtype == LGML_BF16)
-        lgml_launch(poly_norm_kernel<__nv_bfloat16>, n_tokens, ROW_THREADS, 0, stream, z, ldz, coef, (__nv_bfloat16 *)out, ldo, F, eps);
+        lgml_launch(poly_norm_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, z, ldz, coef, (__nv_bfloat16 *)out, ldo, F, eps);
     else LGML_FAIL("poly_norm: unknown output type %d", out_dtype);
     return lgml_launch_status("poly_norm");
 }

@@ -1145,7 +1145,7 @@ def side_add(x: torch.Tensor, y: torch.Tensor, norm_w: torch.Tensor, eps: float,
 
 def sandwich_norm(x: torch.Tensor, w_pre: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor], delta=None,
                   w_post: Optional[torch.Tensor] = None, units=None, row_add: Optional[torch.Tensor] = None,
-                  rows: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+                  rows: Optional[torch.Tensor] = None, conv=None) -> Optional[torch.Tensor]:
     """One kernel over the rows of the float32 residual stream x [tokens, E]:
 
         m   = delta                                               (a float32 tensor), or
@@ -1154,7 +1154,12 @@ def sandwich_norm(x: torch.Tensor, w_pre: Optional[torch.Tensor], eps: float, ou
         out = LN(x) w_pre                                         (``w_pre`` None: no output)
 
     with LN(v) = (v - mean) / sqrt(var + eps), var the mean of the squared deviations.  With ``rows`` (int32 on the
-    device) only those rows are normed and x is not written."""
+    device) only those rows are normed and x is not written.
+
+    ``conv`` = (w_t float32 [taps, E], state float32 [slots, >= (taps - 1) E], slots int32 [tokens]) for a step in which
+    every request brings ONE token (row r is request r's): out = h + sum_j w_t[j] h_(t - taps + 1 + j) with h = LN(x) w_pre,
+    the earlier rows of h from the request's slot, which then takes this one (what ``short_conv`` with ``residual``
+    computes from a float32 h, in the same order)."""
     _need(x, "residual stream", torch.float32, 2)
     n, E = x.shape
     if not x.is_contiguous():
@@ -1186,11 +1191,21 @@ def sandwich_norm(x: torch.Tensor, w_pre: Optional[torch.Tensor], eps: float, ou
             raise KernelError(f"sandwich_norm: output {tuple(out.shape)} is not a contiguous [{n_out}, {E}]")
     if n_out == 0:
         return out if w_pre is not None else None
+    conv_w = conv_state = conv_slots = None
+    taps, ld_state = 0, 0
+    if conv is not None:
+        conv_w, conv_state, conv_slots = conv
+        _need(conv_w, "convolution weights", torch.float32, 2)
+        _need(conv_slots, "slots", torch.int32, 1)
+        taps = conv_w.shape[0]
+        if conv_w.shape[1] != E or not conv_w.is_contiguous() or conv_slots.numel() != n or rows is not None or w_pre is None:
+            raise KernelError("sandwich_norm: the convolution in the same kernel takes [taps, E] weights, one slot per row, all rows and a norm")
+        ld_state = _state_rows(conv_state, (taps - 1) * E, "sandwich_norm") if taps > 1 else 0
     fn = _fn("norm_conv", "lgml_sandwich_norm", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                 c_int, c_int, c_int, c_float, c_void_p])
+                                                 c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_void_p])
     _check("norm_conv", fn(_ptr(x), _ptr(d1), _ptr(d2), _ptr(u1), _ptr(u2), _ptr(w_post), _ptr(row_add), _ptr(w_pre), _ptr(rows),
                            _ptr(out if w_pre is not None else None), dtype_code(out.dtype) if w_pre is not None else F32, n_out, E, float(eps),
-                           _stream()), "sandwich_norm")
+                           _ptr(conv_w), _ptr(conv_state if taps > 1 else None), ld_state, _ptr(conv_slots), taps, _stream()), "sandwich_norm")
     return out if w_pre is not None else None
 
 
@@ -1294,15 +1309,24 @@ def conv_rope_store(proj: torch.Tensor, w_t: torch.Tensor, state: Optional[torch
     return q_out
 
 
+SSD_PIECE_TOKENS = 64      # tokens of a piece when a long portion's recurrence runs in pieces side by side
+
+
 def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor,
-             seq_start: torch.Tensor, slots: torch.Tensor, n_heads: int, n_groups: int, head_dim: int, n_state: int) -> torch.Tensor:
+             seq_start: torch.Tensor, slots: torch.Tensor, n_heads: int, n_groups: int, head_dim: int, n_state: int, pieces=None) -> torch.Tensor:
     """The state-space recurrence of a step's tokens, request by request (all float32):
 
         dt = softplus(dt_raw + dt_bias_h);  S <- exp(-exp(A_log_h) dt) S + dt B x^T;  y = S^T C + D_h x
 
     ``xbc`` [tokens, x (Hs P) | B (G N) | C (G N)] and ``dt_raw`` [tokens, Hs] may be column slices; head h reads group
     h // (Hs / G).  S ([N, P] per head, stored column by column) lives in ``state[slot]`` (float32 [slots, >= Hs P N]).
-    Returns y float32 [tokens, Hs P]."""
+    Returns y float32 [tokens, Hs P].
+
+    ``pieces`` = (int32 [n_pieces, 2] rows (first token row, the row past the last), int32 [requests + 1] the first
+    piece of every request), as ``StepBatch.scan_pieces`` gives them: the pieces run side by side in three launches.
+    Every piece is scanned from zero (what it leaves and the product of its decays are kept), a chain over each
+    request's pieces turns that into the state every piece starts from (and the slot's new state), and every
+    piece is scanned again from there, which gives y."""
     _need(xbc, "convolved x, B and C", torch.float32, 2)
     _need(dt_raw, "step sizes", torch.float32, 2)
     ldx, ldd = _rows_contiguous(xbc, "convolved x, B and C"), _rows_contiguous(dt_raw, "step sizes")
@@ -1318,9 +1342,29 @@ def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, a_l
     y = torch.empty((n, inner), dtype=torch.float32, device=xbc.device)
     n_seqs = seq_start.numel() - 1
     fn = _fn("ssd", "lgml_ssd_scan", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
-                                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
-    _check("ssd", fn(_ptr(xbc), ldx, _ptr(dt_raw), ldd, _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(state), ld_state, _ptr(seq_start), _ptr(slots),
-                     _ptr(y), inner, n_seqs, n_heads, n_groups, head_dim, n_state, _stream()), "ssd_scan")
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+
+    def scan(st, ld, starts, slot_ids, out, count, in_pieces, from_zero, decay):
+        _check("ssd", fn(_ptr(xbc), ldx, _ptr(dt_raw), ldd, _ptr(dt_bias), _ptr(a_log), _ptr(d_skip), _ptr(st), ld, _ptr(starts), _ptr(slot_ids),
+                         _ptr(out), inner, count, n_heads, n_groups, head_dim, n_state, 1 if in_pieces else 0, 1 if from_zero else 0, _ptr(decay),
+                         _stream()), "ssd_scan")
+
+    if pieces is None:
+        scan(state, ld_state, seq_start, slots, y, n_seqs, False, False, None)
+        return y
+    rows, first = pieces
+    _need(rows, "pieces", torch.int32, 2)
+    _need(first, "first pieces", torch.int32, 1)
+    if rows.shape[1] != 2 or not rows.is_contiguous() or first.numel() != n_seqs + 1:
+        raise KernelError("ssd_scan: pieces are a contiguous [n, 2] and one first piece per request and one behind")
+    n_pieces = rows.shape[0]
+    scratch = torch.empty((n_pieces, inner * n_state), dtype=torch.float32, device=xbc.device)
+    decay = torch.empty((n_pieces, n_heads), dtype=torch.float32, device=xbc.device)
+    scan(scratch, inner * n_state, rows, None, None, n_pieces, True, True, decay)
+    chain = _fn("ssd", "lgml_ssd_chain", [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check("ssd", chain(_ptr(scratch), inner * n_state, _ptr(decay), _ptr(state), ld_state, _ptr(first), _ptr(slots), n_seqs, n_heads, head_dim, n_state,
+                        _stream()), "ssd_chain")
+    scan(scratch, inner * n_state, rows, None, y, n_pieces, True, False, None)
     return y
 
 

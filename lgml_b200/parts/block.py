@@ -166,6 +166,9 @@ class SandwichBlock(Part):
         def read(norm, conv, first, floats, pend):
             if conv is None:
                 return norm.forward(rt, x, rt.dtype, delta=pend)
+            if batch.max_q_len == 1 and getattr(norm, "takes_pending", False):
+                # one token a request: the norm's kernel adds the convolution itself
+                return norm.forward(rt, x, rt.dtype, delta=pend, conv=(conv.w_t, state[:, first:first + floats] if floats else None, batch.slots))
             h = norm.forward(rt, x, conv.input_dtype, delta=pend)
             return conv.forward(rt, h, batch, state[:, first:first + floats] if floats else None)
 

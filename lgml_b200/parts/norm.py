@@ -116,7 +116,9 @@ class LayerNorm(Part):
     def bind(self, prefix, tensors, rt):
         self.weight = tensors[prefix + self.suffix].float().contiguous()
 
-    def forward(self, rt, x, out_dtype, delta=None, rows=None):
+    def forward(self, rt, x, out_dtype, delta=None, rows=None, conv=None):
+        """``conv``: (weights [taps, width], state slots, the rows' slots) of a convolution over time of the normed rows that the same
+        kernel adds to them, for a step of one token a request (``ops.sandwich_norm``)."""
         n = x.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.width), dtype=out_dtype, device=x.device)
         pend = delta if isinstance(delta, PendingDelta) else PendingDelta(delta)
@@ -125,7 +127,7 @@ class LayerNorm(Part):
             d = d.sum()
         if isinstance(d, UnitMix):
             d, units = (d.a, d.b), (d.u_a, d.u_b)
-        return ops.sandwich_norm(x, self.weight, self.eps, out, delta=d, w_post=pend.w_post, units=units, row_add=pend.row_add, rows=rows)
+        return ops.sandwich_norm(x, self.weight, self.eps, out, delta=d, w_post=pend.w_post, units=units, row_add=pend.row_add, rows=rows, conv=conv)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

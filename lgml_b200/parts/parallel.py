@@ -37,6 +37,10 @@ from .latent_attention import scaled_frequencies
 from .norm import UnitMix
 
 
+# portions of a request longer than this run the state-space recurrence in pieces side by side
+SSD_PIECES_FROM = 128
+
+
 def _split_specs(spec):
     """(paged spec or None, fixed-state floats) of a mixer's cache spec."""
     specs = spec if isinstance(spec, (tuple, list)) else (spec,)
@@ -164,8 +168,10 @@ class StateSpaceDual(Part):
         xbc = torch.empty((n, C), dtype=torch.float32, device=proj.device)
         ops.short_conv(proj[:, inner:inner + C], self.conv_w, self.conv_b, cache.state[:, self.state_floats:] if self.taps > 1 else None,
                        batch.seq_of_token, batch.seq_start, batch.slots, xbc, act="silu")
+        # a long portion's recurrence runs in pieces side by side
+        pieces = batch.scan_pieces(ops.SSD_PIECE_TOKENS) if batch.max_q_len > SSD_PIECES_FROM else None
         y = ops.ssd_scan(xbc, proj[:, inner + C:inner + C + Hs], self.dt_bias, self.a_log, self.d_skip, cache.state, batch.seq_start, batch.slots,
-                         Hs, self.n_groups, self.head_dim, self.n_state)
+                         Hs, self.n_groups, self.head_dim, self.n_state, pieces=pieces)
         g = ops.ssd_gate_norm(y, proj[:, :inner], self.norm_w, self.norm_groups, self.eps, rt.dtype)
         return rt.linear(g, self.wo, out_dtype=torch.float32)
 

@@ -193,6 +193,21 @@ def test_state_space_scan_whole_in_pieces_and_token_by_token_with_slow_decay(Hs,
             assert np.abs(got[r] - want[r]).max() < 2e-4 * (1 + np.abs(want[r]).max()), f"cuts {cuts[:3]} request {r}"
         assert bool((state[[0, 2]] == 0).all()) and bool((state[:, inner * N:] == 0).all())
     assert share > 0.05
+    # in pieces that run side by side: first 100 tokens of both requests in pieces of 16, then the rest in pieces of 64 beside each other
+    state = torch.zeros((4, inner * N + 5), device=DEV)
+    for (a0, b0), (a1, b1), size in (((0, 100), (0, 30), 16), ((100, 300), (30, 41), 64)):
+        x = np.concatenate([xs[0][a0:b0], xs[1][a1:b1]])
+        dt = np.concatenate([dts[0][a0:b0], dts[1][a1:b1]])
+        rows, first, at = [], [0], 0
+        for n in (b0 - a0, b1 - a1):
+            rows += [(at + t, at + min(t + size, n)) for t in range(0, n, size)]
+            first.append(len(rows))
+            at += n
+        pieces = (torch.tensor(rows, dtype=torch.int32, device=DEV), i32(first))
+        y = ops.ssd_scan(f32(x)[:, :inner + 2 * G * N], f32(dt), f32(dt_bias), f32(a_log), f32(dskip), state, i32([0, b0 - a0, b0 - a0 + b1 - a1]),
+                         i32(slots), Hs, G, Pd, N, pieces=pieces).cpu().numpy()
+        for got_rows, w in ((y[:b0 - a0], want[0][a0:b0]), (y[b0 - a0:], want[1][a1:b1])):
+            assert np.abs(got_rows - w).max() < 2e-4 * (1 + np.abs(w).max()), f"pieces of {size}"
 
 
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
