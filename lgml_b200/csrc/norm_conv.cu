@@ -54,13 +54,14 @@ __device__ __forceinline__ float2 block_sum2(float a, float b, float2 *red) {
     return t;
 }
 
-template <typename TO>
-__global__ void __launch_bounds__(1024) sandwich_norm_kernel(const SandwichArgs a) {
+template <typename TO, int NT>
+__global__ void __launch_bounds__(NT) sandwich_norm_kernel(const SandwichArgs a) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float row[];          // E floats: m, then x
     __shared__ float2 red[32];
-    const int E = a.E, tid = threadIdx.x, nthr = blockDim.x;
+    constexpr int nthr = NT;
+    const int E = a.E, tid = threadIdx.x;
     const int r = blockIdx.x;
     const size_t src = a.rows ? (size_t)a.rows[r] : (size_t)r;
     float *xr = a.x + src * E;
@@ -152,70 +153,148 @@ __device__ __forceinline__ float silu_(float v) { return v / (1.0f + expf(-v)); 
 // of their request read the slot; all of those (the first taps - 1 of the request in this step) are
 // computed by the thread of the request's first token, which then writes the slot: nobody else
 // touches that channel's floats there.
-template <typename TO>
+template <typename TO, int V> struct ConvVec;
+template <typename TO> struct ConvVec<TO, 1> {
+    static __device__ __forceinline__ void load(const float *p, float (&v)[1]) { v[0] = act_load(p); }
+    static __device__ __forceinline__ void load_w(const float *p, float (&v)[1]) { v[0] = __ldg(p); }
+    static __device__ __forceinline__ void store_f(float *p, const float (&v)[1]) { p[0] = v[0]; }
+    static __device__ __forceinline__ void store(TO *p, const float (&v)[1]) { p[0] = from_f32<TO>(v[0]); }
+};
+template <typename TO> struct ConvVec<TO, 4> {
+    static __device__ __forceinline__ void load(const float *p, float (&v)[4]) {
+        const float4 t = act_load(reinterpret_cast<const float4 *>(p));
+        v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+    }
+    static __device__ __forceinline__ void load_w(const float *p, float (&v)[4]) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+        v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+    }
+    static __device__ __forceinline__ void store_f(float *p, const float (&v)[4]) { *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+    static __device__ __forceinline__ void store(float *p, const float (&v)[4]) { store_f(p, v); }
+    static __device__ __forceinline__ void store(__nv_bfloat16 *p, const float (&v)[4]) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        float2 raw;
+        raw.x = *reinterpret_cast<float *>(&lo), raw.y = *reinterpret_cast<float *>(&hi);
+        *reinterpret_cast<float2 *>(p) = raw;
+    }
+};
+
+// V channels a thread (4 when channels, strides and addresses allow 16-byte accesses); TAPS > 0: the taps at compile time
+template <typename TO, int V, int TAPS>
 __global__ void __launch_bounds__(256) short_conv_kernel(const float *__restrict__ u, int ld_in, const float *__restrict__ w,
                                                          const float *__restrict__ bias, float *__restrict__ state, long long state_ld,
                                                          const int *__restrict__ seq_of_token, const int *__restrict__ seq_start,
-                                                         const int *__restrict__ slots, TO *__restrict__ out, int ld_out, int n, int C, int taps,
+                                                         const int *__restrict__ slots, TO *__restrict__ out, int ld_out, int n, int C, int taps_rt,
                                                          int act, int residual) {
     pdl_trigger();
     pdl_wait();
-    const size_t total = (size_t)n * C;
+    using X = ConvVec<TO, V>;
+    const int taps = TAPS > 0 ? TAPS : taps_rt;
+    constexpr int MT = TAPS > 0 ? TAPS : MAX_TAPS;
+    const int per_row = C / V;
+    const size_t total = (size_t)n * per_row;
     const int back = taps - 1;
     for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += (size_t)gridDim.x * blockDim.x) {
-        const int t = (int)(it / C), c = (int)(it - (size_t)t * C);
+        const int t = (int)(it / per_row), c = (int)(it - (size_t)t * per_row) * V;
         const int s = seq_of_token[t];
         const int t0 = seq_start[s];
         const int i = t - t0;
         if (i > 0 && i < back) continue;
-        float wj[MAX_TAPS];
-        for (int j = 0; j < taps; ++j) wj[j] = __ldg(w + (size_t)j * C + c);
-        const float b = bias ? __ldg(bias + c) : 0.f;
+        float b[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) b[e] = 0.f;
+        if (bias) X::load_w(bias + c, b);
         if (i >= back) {
-            float acc = b, cur = 0.f;
-            for (int j = 0; j < taps; ++j) {
-                cur = act_load(u + (size_t)(t - back + j) * ld_in + c);
-                acc = fmaf(wj[j], cur, acc);
+            float in[MT][V], wj[MT][V];
+#pragma unroll
+            for (int j = 0; j < MT; ++j)
+                if (j < taps) X::load(u + (size_t)(t - back + j) * ld_in + c, in[j]), X::load_w(w + (size_t)j * C + c, wj[j]);
+            float y[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                float acc = b[e], cur = 0.f;
+#pragma unroll
+                for (int j = 0; j < MT; ++j)
+                    if (j < taps) cur = in[j][e], acc = fmaf(wj[j][e], cur, acc);
+                if (act == 1) acc = silu_(acc);
+                if (residual) acc += cur;
+                y[e] = acc;
             }
-            if (act == 1) acc = silu_(acc);
-            if (residual) acc += cur;
-            out[(size_t)t * ld_out + c] = from_f32<TO>(acc);
+            X::store(out + (size_t)t * ld_out + c, y);
             continue;
         }
         // the request's first token of this step
         const int n_s = seq_start[s + 1] - t0;
         float *st = state + (size_t)slots[s] * state_ld + c;
-        float old[MAX_TAPS];
-        for (int r = 0; r < back; ++r) old[r] = act_load(st + (size_t)r * C);
+        float old[MT][V], wj[MT][V];
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+            if (j < back) X::load(st + (size_t)j * C, old[j]);
+            if (j < taps) X::load_w(w + (size_t)j * C + c, wj[j]);
+        }
         const int first = n_s < back ? n_s : back;
         for (int k = 0; k < first; ++k) {
-            float acc = b, cur = 0.f;
-            for (int j = 0; j < taps; ++j) {
-                const int rel = k - back + j;
-                cur = rel >= 0 ? act_load(u + (size_t)(t0 + rel) * ld_in + c) : old[back + rel];
-                acc = fmaf(wj[j], cur, acc);
+            float y[V], acc[V], cur[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[e] = b[e], cur[e] = 0.f;
+#pragma unroll
+            for (int j = 0; j < MT; ++j) {
+                if (j < taps) {
+                    const int rel = k - back + j;
+                    if (rel >= 0) {
+                        X::load(u + (size_t)(t0 + rel) * ld_in + c, cur);
+                    } else {
+#pragma unroll
+                        for (int r = 0; r < MT; ++r)
+                            if (r == back + rel) {
+#pragma unroll
+                                for (int e = 0; e < V; ++e) cur[e] = old[r][e];
+                            }
+                    }
+#pragma unroll
+                    for (int e = 0; e < V; ++e) acc[e] = fmaf(wj[j][e], cur[e], acc[e]);
+                }
             }
-            if (act == 1) acc = silu_(acc);
-            if (residual) acc += cur;
-            out[(size_t)(t0 + k) * ld_out + c] = from_f32<TO>(acc);
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                float a2 = acc[e];
+                if (act == 1) a2 = silu_(a2);
+                if (residual) a2 += cur[e];
+                y[e] = a2;
+            }
+            X::store(out + (size_t)(t0 + k) * ld_out + c, y);
         }
-        for (int r = 0; r < back; ++r) {
-            const int rel = n_s - back + r;
-            st[(size_t)r * C] = rel >= 0 ? act_load(u + (size_t)(t0 + rel) * ld_in + c) : old[back + rel];
+#pragma unroll
+        for (int r = 0; r < MT; ++r) {
+            if (r < back) {
+                const int rel = n_s - back + r;
+                float v[V];
+                if (rel >= 0) {
+                    X::load(u + (size_t)(t0 + rel) * ld_in + c, v);
+                } else {
+#pragma unroll
+                    for (int q = 0; q < MT; ++q)
+                        if (q == back + rel) {
+#pragma unroll
+                            for (int e = 0; e < V; ++e) v[e] = old[q][e];
+                        }
+                }
+                X::store_f(st + (size_t)r * C, v);
+            }
         }
     }
 }
 
 // z float32 [n, F] -> out [n, F]; coef float32 [4] = a, b, c, e
-template <typename TO>
-__global__ void __launch_bounds__(1024) poly_norm_kernel(const float *__restrict__ z, int ldz, const float *__restrict__ coef,
+template <typename TO, int NT>
+__global__ void __launch_bounds__(NT) poly_norm_kernel(const float *__restrict__ z, int ldz, const float *__restrict__ coef,
                                                                 TO *__restrict__ out, int ldo, int F, float eps) {
     pdl_trigger();
     pdl_wait();
     __shared__ float red[32];
     const float *zr = z + (size_t)blockIdx.x * ldz;
     float s1 = 0.f, s2 = 0.f, s3 = 0.f;
-    for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    for (int i = threadIdx.x; i < F; i += NT) {
         const float v = act_load(zr + i), v2 = v * v;
         s1 += v2, s2 = fmaf(v2, v2, s2), s3 = fmaf(v2 * v2, v2, s3);
     }
@@ -224,7 +303,7 @@ __global__ void __launch_bounds__(1024) poly_norm_kernel(const float *__restrict
     const float a = __ldg(coef) / sqrtf(s1 * invF + eps), b = __ldg(coef + 1) / sqrtf(s2 * invF + eps),
                 c = __ldg(coef + 2) / sqrtf(s3 * invF + eps), e = __ldg(coef + 3);
     TO *orow = out + (size_t)blockIdx.x * ldo;
-    for (int i = threadIdx.x; i < F; i += blockDim.x) {
+    for (int i = threadIdx.x; i < F; i += NT) {
         const float v = act_load(zr + i);
         orow[i] = from_f32<TO>(fmaf(v, fmaf(v, fmaf(v, c, b), a), e));
     }
@@ -252,15 +331,15 @@ LGML_API int lgml_sandwich_norm(float *x, const float *d1, const float *d2, cons
     const size_t smem = (size_t)E * sizeof(float);
     // few rows (a decode step): a row's passes are latency, so more threads share it; many rows: blocks of 256 fill the SMs
     const int threads = (n_out <= 296 && E >= 1024) ? 1024 : ROW_THREADS;
-    if (out_dtype == LGML_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(sandwich_norm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lgml_launch(sandwich_norm_kernel<float>, n_out, threads, smem, stream, a);
-    } else if (out_dtype == LGML_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(sandwich_norm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        lgml_launch(sandwich_norm_kernel<__nv_bfloat16>, n_out, threads, smem, stream, a);
-    } else {
-        LGML_FAIL("sandwich_norm: unknown output type %d", out_dtype);
-    }
+#define LGML_SN(TO, NT)                                                                                                          \
+    do {                                                                                                                         \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(sandwich_norm_kernel<TO, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        lgml_launch(sandwich_norm_kernel<TO, NT>, n_out, NT, smem, stream, a);                                                 \
+    } while (0)
+    if (out_dtype == LGML_F32) { if (threads == 1024) LGML_SN(float, 1024); else LGML_SN(float, ROW_THREADS); }
+    else if (out_dtype == LGML_BF16) { if (threads == 1024) LGML_SN(__nv_bfloat16, 1024); else LGML_SN(__nv_bfloat16, ROW_THREADS); }
+    else LGML_FAIL("sandwich_norm: unknown output type %d", out_dtype);
+#undef LGML_SN
     return lgml_launch_status("sandwich_norm");
 }
 
@@ -271,12 +350,17 @@ LGML_API int lgml_short_conv(const float *u, int ld_in, const float *w, const fl
     LGML_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "short_conv: 1 to %d taps, not %d", MAX_TAPS, taps);
     LGML_REQUIRE(taps == 1 || (state != nullptr && state_ld >= (long long)(taps - 1) * C), "short_conv: the state's rows do not hold taps - 1 inputs");
     if (n_tokens == 0) return 0;
-    const int grid = grid_for((size_t)n_tokens * C, 256);
-#define LGML_SC(TO) lgml_launch(short_conv_kernel<TO>, grid, 256, 0, stream, u, ld_in, w, bias, state, state_ld, seq_of_token, seq_start, slots, \
-                                (TO *)out, ld_out, n_tokens, C, taps, act, residual)
-    if (out_dtype == LGML_F32) LGML_SC(float);
-    else if (out_dtype == LGML_BF16) LGML_SC(__nv_bfloat16);
+    const bool vec = C % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && state_ld % 4 == 0 &&
+                     ((((uintptr_t)u | (uintptr_t)w | (uintptr_t)bias | (uintptr_t)state) & 15) == 0) && (((uintptr_t)out & 15) == 0);
+    const int grid = grid_for((size_t)n_tokens * (vec ? C / 4 : C), 256);
+#define LGML_SC(TO, V, T) lgml_launch(short_conv_kernel<TO, V, T>, grid, 256, 0, stream, u, ld_in, w, bias, state, state_ld, seq_of_token, seq_start, \
+                                      slots, (TO *)out, ld_out, n_tokens, C, taps, act, residual)
+#define LGML_SC_T(TO, V) \
+    switch (taps) { case 2: LGML_SC(TO, V, 2); break; case 3: LGML_SC(TO, V, 3); break; case 4: LGML_SC(TO, V, 4); break; default: LGML_SC(TO, V, 0); }
+    if (out_dtype == LGML_F32) { if (vec) { LGML_SC_T(float, 4) } else { LGML_SC_T(float, 1) } }
+    else if (out_dtype == LGML_BF16) { if (vec) { LGML_SC_T(__nv_bfloat16, 4) } else { LGML_SC_T(__nv_bfloat16, 1) } }
     else LGML_FAIL("short_conv: unknown output type %d", out_dtype);
+#undef LGML_SC_T
 #undef LGML_SC
     return lgml_launch_status("short_conv");
 }
@@ -286,9 +370,10 @@ LGML_API int lgml_poly_norm(const float *z, int ldz, const float *coef, void *ou
     LGML_REQUIRE(n_tokens >= 0 && F > 0 && ldz >= F && ldo >= F, "poly_norm: bad sizes");
     if (n_tokens == 0) return 0;
     const int threads = (n_tokens <= 296 && F >= 1024) ? 1024 : ROW_THREADS;      // few rows: more threads share a row's latency
-    if (out_dtype == LGML_F32) lgml_launch(poly_norm_kernel<float>, n_tokens, threads, 0, stream, z, ldz, coef, (float *)out, ldo, F, eps);
-    else if (out_dtype == LGML_BF16)
-        lgml_launch(poly_norm_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, z, ldz, coef, (__nv_bfloat16 *)out, ldo, F, eps);
+#define LGML_PN(TO, NT) lgml_launch(poly_norm_kernel<TO, NT>, n_tokens, NT, 0, stream, z, ldz, coef, (TO *)out, ldo, F, eps)
+    if (out_dtype == LGML_F32) { if (threads == 1024) LGML_PN(float, 1024); else LGML_PN(float, ROW_THREADS); }
+    else if (out_dtype == LGML_BF16) { if (threads == 1024) LGML_PN(__nv_bfloat16, 1024); else LGML_PN(__nv_bfloat16, ROW_THREADS); }
     else LGML_FAIL("poly_norm: unknown output type %d", out_dtype);
+#undef LGML_PN
     return lgml_launch_status("poly_norm");
 }
