@@ -346,7 +346,7 @@ def dizepel_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int,
     dense feed-forward of the full inner width (as many weights as the gated one of two thirds of it); four taps on what
     the sublayers read; no loop (the Llama decoder beside it runs every layer once)."""
     left = {"heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "conv": 4, "scale": head_dim ** -0.5, "softcap": 30.0,
-            "rot": {"base": 250000.0, "dims": head_dim // 2, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+            "rot": {"base": 500000.0, "dims": head_dim // 2, "scaling": {"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 1.0}}}
     right = {"heads": width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
     layer = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": {"kind": "dense", "ff": ff}}
     return {"architecture": "Dizepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "canon": {"taps": 4},

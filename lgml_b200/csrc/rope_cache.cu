@@ -251,21 +251,51 @@ int launch(const void *src, int lds, int n_parts, long long part_stride, const f
 // writes the slot (no other item touches its floats there).
 constexpr int CONV_MAX_TAPS = 8;
 
-template <typename T>
+template <int V> struct CrsVec;
+template <> struct CrsVec<1> {
+    static __device__ __forceinline__ void load(const float *p, float (&v)[1]) { v[0] = act_load(p); }
+    static __device__ __forceinline__ void load_w(const float *p, float (&v)[1]) { v[0] = __ldg(p); }
+    static __device__ __forceinline__ void store(float *p, const float (&v)[1]) { p[0] = v[0]; }
+    static __device__ __forceinline__ void store(__nv_bfloat16 *p, const float (&v)[1]) { p[0] = __float2bfloat16_rn(v[0]); }
+};
+template <> struct CrsVec<4> {
+    static __device__ __forceinline__ void load(const float *p, float (&v)[4]) {
+        const float4 t = act_load(reinterpret_cast<const float4 *>(p));
+        v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+    }
+    static __device__ __forceinline__ void load_w(const float *p, float (&v)[4]) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+        v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+    }
+    static __device__ __forceinline__ void store(float *p, const float (&v)[4]) { *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+    static __device__ __forceinline__ void store(__nv_bfloat16 *p, const float (&v)[4]) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+        float2 raw;
+        raw.x = *reinterpret_cast<float *>(&lo), raw.y = *reinterpret_cast<float *>(&hi);
+        *reinterpret_cast<float2 *>(p) = raw;
+    }
+};
+
+// V: neighbouring pairs (or unrotated entries) a work item takes: 4 when sizes, strides and addresses allow 16-byte
+// loads and 8-byte stores, else 1.
+template <typename T, int V, int TAPS>
 __global__ void __launch_bounds__(ITEMS) conv_rope_store_kernel(
-    const float *__restrict__ proj, int ldp, const float *__restrict__ wT, float *__restrict__ state, long long state_ld, int taps,
+    const float *__restrict__ proj, int ldp, const float *__restrict__ wT, float *__restrict__ state, long long state_ld, int taps_rt,
     T *__restrict__ q_out, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token, const int *__restrict__ seq_start,
     const int *__restrict__ slots, const int *__restrict__ block_table, int max_blocks, const float *__restrict__ inv_freq,
     const float *__restrict__ inv_freq_lo, float mag, int n_rot, T *__restrict__ k_pages, T *__restrict__ v_pages, int n_pages, int page_size,
     int H, int G, int D, int Dv, int write_kv, int *__restrict__ status) {
     pdl_trigger();
     pdl_wait();
+    using X = CrsVec<V>;
+    const int taps = TAPS > 0 ? TAPS : taps_rt;
+    constexpr int MT = TAPS > 0 ? TAPS : CONV_MAX_TAPS;      // TAPS > 0: the taps at compile time
     const int t = blockIdx.x;
-    const int half_rot = n_rot / 2, iph = half_rot + (D - n_rot);
+    const int half_rot = n_rot / 2, iph = (half_rot + (D - n_rot)) / V;
     const int n_heads = write_kv ? H + G : H;
     const int item = blockIdx.y * ITEMS + threadIdx.x;
     if (item >= n_heads * iph) return;
-    const int head = item / iph, j = item - head * iph;
+    const int head = item / iph, j = (item - head * iph) * V;
     const int s = seq_of_token[t];
     const int t0 = seq_start[s];
     const int i = t - t0, back = taps - 1;
@@ -273,26 +303,34 @@ __global__ void __launch_bounds__(ITEMS) conv_rope_store_kernel(
     const int d0 = j < half_rot ? j : n_rot + (j - half_rot);
     const int d1 = j < half_rot ? j + half_rot : -1;
     const bool two = d1 >= 0;
-    const float f = two ? inv_freq[j] : 0.f, f_lo = (two && inv_freq_lo) ? inv_freq_lo[j] : 0.f;
+    float f[V], f_lo[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) f[e] = two ? inv_freq[j + e] : 0.f, f_lo[e] = (two && inv_freq_lo) ? inv_freq_lo[j + e] : 0.f;
     const int C = (H + G) * D;
     const int c0 = head * D + d0, c1 = head * D + (two ? d1 : d0);
-    float w0[CONV_MAX_TAPS], w1[CONV_MAX_TAPS];
-    for (int k = 0; k < taps; ++k) w0[k] = __ldg(wT + (size_t)k * C + c0), w1[k] = __ldg(wT + (size_t)k * C + c1);
+    float w0[MT][V], w1[MT][V];
+#pragma unroll
+    for (int k = 0; k < MT; ++k)
+        if (k < taps) X::load_w(wT + (size_t)k * C + c0, w0[k]), X::load_w(wT + (size_t)k * C + c1, w1[k]);
 
-    auto emit = [&](int tt, float a, float b) {
+    auto emit = [&](int tt, const float (&a)[V], const float (&b)[V]) {
         const int pos = positions[tt];
-        float ra = a, rb = b;
-        if (two) {
-            float sn, cs;
-            rope_sincos(pos, f, f_lo, &sn, &cs);
-            sn *= mag, cs *= mag;
-            ra = a * cs - b * sn;
-            rb = b * cs + a * sn;
+        float ra[V], rb[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            ra[e] = a[e], rb[e] = b[e];
+            if (two) {
+                float sn, cs;
+                rope_sincos(pos, f[e], f_lo[e], &sn, &cs);
+                sn *= mag, cs *= mag;
+                ra[e] = a[e] * cs - b[e] * sn;
+                rb[e] = b[e] * cs + a[e] * sn;
+            }
         }
         if (head < H) {
             T *qr = q_out + (size_t)tt * ldq + (size_t)head * D;
-            qr[d0] = from_f32<T>(ra);
-            if (two) qr[d1] = from_f32<T>(rb);
+            X::store(qr + d0, ra);
+            if (two) X::store(qr + d1, rb);
             return;
         }
         const int g = head - H;
@@ -304,44 +342,96 @@ __global__ void __launch_bounds__(ITEMS) conv_rope_store_kernel(
             return;
         }
         const size_t cell = ((size_t)page * G + g) * page_size + (size_t)(pos % page_size);
-        k_pages[cell * D + d0] = from_f32<T>(ra);
-        if (two) k_pages[cell * D + d1] = from_f32<T>(rb);
-        if (d0 < Dv) v_pages[cell * Dv + d0] = from_f32<T>(a);
-        if (two && d1 < Dv) v_pages[cell * Dv + d1] = from_f32<T>(b);
+        X::store(k_pages + cell * D + d0, ra);
+        if (two) X::store(k_pages + cell * D + d1, rb);
+        if (d0 < Dv) X::store(v_pages + cell * Dv + d0, a);          // (with V = 4 the value size is a multiple of 4: a group lies inside or outside)
+        if (two && d1 < Dv) X::store(v_pages + cell * Dv + d1, b);
     };
 
     if (i >= back) {
-        float a = 0.f, b = 0.f;
-        for (int k = 0; k < taps; ++k) {
-            const float *row = proj + (size_t)(t - back + k) * ldp;
-            a = fmaf(w0[k], act_load(row + c0), a);
-            if (two) b = fmaf(w1[k], act_load(row + c1), b);
+        float a[V], b[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) a[e] = b[e] = 0.f;
+#pragma unroll
+        for (int k = 0; k < MT; ++k) {
+            if (k < taps) {
+                const float *row = proj + (size_t)(t - back + k) * ldp;
+                float u0[V], u1[V];
+                X::load(row + c0, u0);
+                if (two) X::load(row + c1, u1);
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    a[e] = fmaf(w0[k][e], u0[e], a[e]);
+                    if (two) b[e] = fmaf(w1[k][e], u1[e], b[e]);
+                }
+            }
         }
         emit(t, a, b);
         return;
     }
     const int n_s = seq_start[s + 1] - t0;
     float *st = state + (size_t)slots[s] * state_ld;
-    float old0[CONV_MAX_TAPS], old1[CONV_MAX_TAPS];
-    for (int r = 0; r < back; ++r) old0[r] = act_load(st + (size_t)r * C + c0), old1[r] = two ? act_load(st + (size_t)r * C + c1) : 0.f;
+    float old0[MT][V], old1[MT][V];
+#pragma unroll
+    for (int r = 0; r < MT; ++r) {
+        if (r < back) {
+            X::load(st + (size_t)r * C + c0, old0[r]);
+            if (two) X::load(st + (size_t)r * C + c1, old1[r]);
+        }
+    }
     const int first = n_s < back ? n_s : back;
     for (int kk = 0; kk < first; ++kk) {
-        float a = 0.f, b = 0.f;
-        for (int k = 0; k < taps; ++k) {
-            const int rel = kk - back + k;
-            const float u0 = rel >= 0 ? act_load(proj + (size_t)(t0 + rel) * ldp + c0) : old0[back + rel];
-            a = fmaf(w0[k], u0, a);
-            if (two) {
-                const float u1 = rel >= 0 ? act_load(proj + (size_t)(t0 + rel) * ldp + c1) : old1[back + rel];
-                b = fmaf(w1[k], u1, b);
+        float a[V], b[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) a[e] = b[e] = 0.f;
+#pragma unroll
+        for (int k = 0; k < MT; ++k) {
+            if (k < taps) {
+                const int rel = kk - back + k;
+                float u0[V], u1[V];
+#pragma unroll
+                for (int e = 0; e < V; ++e) u0[e] = u1[e] = 0.f;
+                if (rel >= 0) {
+                    X::load(proj + (size_t)(t0 + rel) * ldp + c0, u0);
+                    if (two) X::load(proj + (size_t)(t0 + rel) * ldp + c1, u1);
+                } else {
+#pragma unroll
+                    for (int r = 0; r < MT; ++r)
+                        if (r == back + rel) {
+#pragma unroll
+                            for (int e = 0; e < V; ++e) u0[e] = old0[r][e], u1[e] = two ? old1[r][e] : 0.f;
+                        }
+                }
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    a[e] = fmaf(w0[k][e], u0[e], a[e]);
+                    if (two) b[e] = fmaf(w1[k][e], u1[e], b[e]);
+                }
             }
         }
         emit(t0 + kk, a, b);
     }
-    for (int r = 0; r < back; ++r) {
-        const int rel = n_s - back + r;
-        st[(size_t)r * C + c0] = rel >= 0 ? act_load(proj + (size_t)(t0 + rel) * ldp + c0) : old0[back + rel];
-        if (two) st[(size_t)r * C + c1] = rel >= 0 ? act_load(proj + (size_t)(t0 + rel) * ldp + c1) : old1[back + rel];
+#pragma unroll
+    for (int r = 0; r < MT; ++r) {
+        if (r < back) {
+            const int rel = n_s - back + r;
+            float v0[V], v1[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) v0[e] = v1[e] = 0.f;
+            if (rel >= 0) {
+                X::load(proj + (size_t)(t0 + rel) * ldp + c0, v0);
+                if (two) X::load(proj + (size_t)(t0 + rel) * ldp + c1, v1);
+            } else {
+#pragma unroll
+                for (int q = 0; q < MT; ++q)
+                    if (q == back + rel) {
+#pragma unroll
+                        for (int e = 0; e < V; ++e) v0[e] = old0[q][e], v1[e] = two ? old1[q][e] : 0.f;
+                    }
+            }
+            X::store(st + (size_t)r * C + c0, v0);
+            if (two) X::store(st + (size_t)r * C + c1, v1);
+        }
     }
 }
 }  // namespace
@@ -394,15 +484,20 @@ LGML_API int lgml_conv_rope_store(const float *proj, int ldp, const float *wT, f
     LGML_REQUIRE(taps == 1 || (state != nullptr && state_ld >= (long long)(taps - 1) * (H + G) * D), "conv_rope_store: the state's rows are too short");
     LGML_REQUIRE(ldp >= (H + G) * D && ldq >= H * D, "conv_rope_store: rows too short");
     if (n_tokens == 0) return 0;
-    const int iph = n_rot / 2 + (D - n_rot);
+    const bool vec = (n_rot / 2) % 4 == 0 && (D - n_rot) % 4 == 0 && Dv % 4 == 0 && ldp % 4 == 0 && ldq % 4 == 0 && state_ld % 4 == 0 &&
+                     ((((uintptr_t)proj | (uintptr_t)wT | (uintptr_t)state | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0);
+    const int iph = (n_rot / 2 + (D - n_rot)) / (vec ? 4 : 1);
     const int items = (write_kv ? H + G : H) * iph;
     dim3 grid(n_tokens, (items + ITEMS - 1) / ITEMS);
-#define LGML_CRS(T) lgml_launch(conv_rope_store_kernel<T>, grid, ITEMS, 0, stream, proj, ldp, wT, state, state_ld, taps, (T *)q_out, ldq, positions, \
-                                seq_of_token, seq_start, slots, block_table, max_blocks, inv_freq, inv_freq_lo, mag, n_rot, (T *)k_pages, (T *)v_pages, \
-                                n_pages, page_size, H, G, D, Dv, write_kv, status)
-    if (dtype == LGML_F32) LGML_CRS(float);
-    else if (dtype == LGML_BF16) LGML_CRS(__nv_bfloat16);
+#define LGML_CRS_T(T, V, TP) lgml_launch(conv_rope_store_kernel<T, V, TP>, grid, ITEMS, 0, stream, proj, ldp, wT, state, state_ld, taps, (T *)q_out, ldq, positions, \
+                                   seq_of_token, seq_start, slots, block_table, max_blocks, inv_freq, inv_freq_lo, mag, n_rot, (T *)k_pages, (T *)v_pages, \
+                                   n_pages, page_size, H, G, D, Dv, write_kv, status)
+#define LGML_CRS(T, V) \
+    do { switch (taps) { case 2: LGML_CRS_T(T, V, 2); break; case 3: LGML_CRS_T(T, V, 3); break; case 4: LGML_CRS_T(T, V, 4); break; default: LGML_CRS_T(T, V, 0); } } while (0)
+    if (dtype == LGML_F32) { if (vec) LGML_CRS(float, 4); else LGML_CRS(float, 1); }
+    else if (dtype == LGML_BF16) { if (vec) LGML_CRS(__nv_bfloat16, 4); else LGML_CRS(__nv_bfloat16, 1); }
     else LGML_FAIL("conv_rope_store: unknown type %d", dtype);
 #undef LGML_CRS
+#undef LGML_CRS_T
     return lgml_launch_status("conv_rope_store");
 }

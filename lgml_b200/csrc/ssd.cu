@@ -24,12 +24,13 @@ __device__ __forceinline__ float silu_(float v) { return v / (1.0f + expf(-v)); 
 
 // xbc float32 [n, ldx]: x of head h at column h P, B of group g at column x_cols + g N, C at x_cols + (G + g) N.
 // dt_raw float32 [n, ldd], column h.  state: per slot [Hs][P][N].  y float32 [n, ldy], column h P + p.
-// Block: (column tile, head, request); a column's N entries are dealt over LN neighbouring lanes, RN each, in groups
-// of four: lane l owns the groups l, l + LN, l + 2 LN ..., so the LN lanes of a column read neighbouring 16-byte
-// pieces of a token's B and C from shared memory (no bank is asked twice) and of the state from memory.
+// Block: (column tile, head, request).  A thread owns RN entries of each of CQ neighbouring columns: what it reads of
+// a token's B and C serves CQ columns (the shared-memory reads are what bounds this kernel).  A column's N entries are
+// dealt over LN neighbouring lanes in groups of four: lane l owns the groups l, l + LN, l + 2 LN ..., so the lanes
+// read neighbouring 16-byte pieces of B and C from shared memory (no bank is asked twice) and of the state from memory.
 // The step's tokens come through shared memory in groups of TT: B, C (rows of NS = LN RN floats, zeros behind N),
 // the tile's x, dt and the decay.
-template <int RN>
+template <int RN, int CQ>
 __global__ void __launch_bounds__(SCAN_THREADS) ssd_scan_kernel(const float *__restrict__ xbc, int ldx, const float *__restrict__ dt_raw, int ldd,
                                                                 const float *__restrict__ dt_bias, const float *__restrict__ a_log,
                                                                 const float *__restrict__ d_skip, float *__restrict__ state, long long state_ld,
@@ -39,21 +40,23 @@ __global__ void __launch_bounds__(SCAN_THREADS) ssd_scan_kernel(const float *__r
     pdl_trigger();
     pdl_wait();
     extern __shared__ float sm[];
-    const int CPB = SCAN_THREADS / LN;
+    const int CPB = (SCAN_THREADS / LN) * CQ;          // columns of a block
     const int NS = LN * RN;
     float *Bs = sm, *Cs = Bs + (size_t)TT * NS, *xs = Cs + (size_t)TT * NS, *dts = xs + (size_t)TT * CPB, *dAs = dts + TT;
     const int h = blockIdx.y, s = blockIdx.z, g = h / (Hs / G);
     const int tid = threadIdx.x, col = tid / LN, ln = tid - col * LN;
-    const int p = blockIdx.x * CPB + col;
+    const int p0 = blockIdx.x * CPB + col * CQ;        // this thread's first column
     auto n_of = [&](int i) { return ((i >> 2) * LN + ln) * 4 + (i & 3); };      // the state entry behind this lane's i-th register
     // pieces: the step's tokens in pieces of consecutive tokens, rows (first, past the last) of an [n, 2] table
     const int t0 = pieces ? seq_start[2 * s] : seq_start[s], t1 = pieces ? seq_start[2 * s + 1] : seq_start[s + 1];
     const int x_cols = Hs * P;
     const float a = expf(__ldg(a_log + h)), bias = __ldg(dt_bias + h), dsk = __ldg(d_skip + h);
-    float *st = state + (size_t)(slots ? slots[s] : s) * state_ld + ((size_t)h * P + (p < P ? p : 0)) * N;
-    float S[RN];
+    float *st = state + (size_t)(slots ? slots[s] : s) * state_ld + (size_t)h * P * N;
+    float S[CQ][RN];
 #pragma unroll
-    for (int i = 0; i < RN; ++i) S[i] = (!zero_start && p < P && n_of(i) < N) ? act_load(st + n_of(i)) : 0.f;
+    for (int q = 0; q < CQ; ++q)
+#pragma unroll
+        for (int i = 0; i < RN; ++i) S[q][i] = (!zero_start && p0 + q < P && n_of(i) < N) ? act_load(st + (size_t)(p0 + q) * N + n_of(i)) : 0.f;
     float decay = 1.f;
     const bool want_y = y != nullptr;
     for (int tb = t0; tb < t1; tb += TT) {
@@ -103,32 +106,45 @@ __global__ void __launch_bounds__(SCAN_THREADS) ssd_scan_kernel(const float *__r
         }
         __syncthreads();
         for (int k = 0; k < nt; ++k) {
-            const float xv = xs[k * CPB + col], dA = dAs[k], dx = dts[k] * xv;
+            const float dA = dAs[k], dt = dts[k];
+            float xv[CQ], dx[CQ], acc[CQ];
+#pragma unroll
+            for (int q = 0; q < CQ; ++q) xv[q] = xs[k * CPB + col * CQ + q], dx[q] = dt * xv[q], acc[q] = 0.f;
             decay *= dA;
             const float4 *Bk = reinterpret_cast<const float4 *>(Bs + (size_t)k * NS) + ln, *Ck = reinterpret_cast<const float4 *>(Cs + (size_t)k * NS) + ln;
-            float acc = 0.f;
 #pragma unroll
             for (int j = 0; j < RN / 4; ++j) {
                 const float4 b = Bk[j * LN];
-                S[4 * j] = fmaf(dA, S[4 * j], dx * b.x), S[4 * j + 1] = fmaf(dA, S[4 * j + 1], dx * b.y);
-                S[4 * j + 2] = fmaf(dA, S[4 * j + 2], dx * b.z), S[4 * j + 3] = fmaf(dA, S[4 * j + 3], dx * b.w);
+#pragma unroll
+                for (int q = 0; q < CQ; ++q) {
+                    S[q][4 * j] = fmaf(dA, S[q][4 * j], dx[q] * b.x), S[q][4 * j + 1] = fmaf(dA, S[q][4 * j + 1], dx[q] * b.y);
+                    S[q][4 * j + 2] = fmaf(dA, S[q][4 * j + 2], dx[q] * b.z), S[q][4 * j + 3] = fmaf(dA, S[q][4 * j + 3], dx[q] * b.w);
+                }
                 if (want_y) {
                     const float4 c = Ck[j * LN];
-                    acc = fmaf(S[4 * j], c.x, acc), acc = fmaf(S[4 * j + 1], c.y, acc);
-                    acc = fmaf(S[4 * j + 2], c.z, acc), acc = fmaf(S[4 * j + 3], c.w, acc);
+#pragma unroll
+                    for (int q = 0; q < CQ; ++q) {
+                        acc[q] = fmaf(S[q][4 * j], c.x, acc[q]), acc[q] = fmaf(S[q][4 * j + 1], c.y, acc[q]);
+                        acc[q] = fmaf(S[q][4 * j + 2], c.z, acc[q]), acc[q] = fmaf(S[q][4 * j + 3], c.w, acc[q]);
+                    }
                 }
             }
             if (want_y) {
-                for (int o = LN >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                if (ln == 0 && p < P) y[(size_t)(tb + k) * ldy + (size_t)h * P + p] = fmaf(dsk, xv, acc);
+#pragma unroll
+                for (int q = 0; q < CQ; ++q) {
+                    for (int o = LN >> 1; o > 0; o >>= 1) acc[q] += __shfl_xor_sync(0xffffffffu, acc[q], o);
+                    if (ln == 0 && p0 + q < P) y[(size_t)(tb + k) * ldy + (size_t)h * P + p0 + q] = fmaf(dsk, xv[q], acc[q]);
+                }
             }
         }
     }
-    if (p < P) {
 #pragma unroll
-        for (int i = 0; i < RN; ++i)
-            if (n_of(i) < N) st[n_of(i)] = S[i];
-    }
+    for (int q = 0; q < CQ; ++q)
+        if (p0 + q < P) {
+#pragma unroll
+            for (int i = 0; i < RN; ++i)
+                if (n_of(i) < N) st[(size_t)(p0 + q) * N + n_of(i)] = S[q][i];
+        }
     if (decay_out != nullptr && blockIdx.x == 0 && tid == 0) decay_out[(size_t)s * Hs + h] = decay;
 }
 
@@ -198,30 +214,43 @@ LGML_API int lgml_ssd_scan(const float *xbc, int ldx, const float *dt_raw, int l
     LGML_REQUIRE(n_seqs <= 65535 && Hs <= 65535, "ssd_scan: too many requests, pieces or heads");
     LGML_REQUIRE(slots != nullptr || pieces, "ssd_scan: requests come with their slots");
     if (n_seqs == 0) return 0;
-    // RN entries a lane, LN lanes a column (a power of two up to 32): the pair that wastes least, then the smaller RN
-    static const int rns[5] = {8, 12, 16, 24, 32};
+    // RN entries a lane, LN lanes a column (a power of two up to 32): the pair that wastes least, then the smaller RN.
+    // Four columns a thread with up to 16 entries each (states up to 512 numbers a column), else one column with up to 32.
+    const bool quad = N <= 512;
+    static const int rns[6] = {4, 8, 12, 16, 24, 32};
     int best_rn = 32, best_ln = 32, best_cover = 1 << 30;
-    for (int i = 0; i < 5; ++i) {
+    for (int i = 0; i < 6; ++i) {
+        if (quad ? rns[i] > 16 : rns[i] < 8) continue;
         int ln = 1;
         while (ln * rns[i] < N && ln < 32) ln *= 2;
         if (ln * rns[i] < N) continue;
-        if (ln * rns[i] < best_cover) best_cover = ln * rns[i], best_rn = rns[i], best_ln = ln;
+        // (at equal cover: with four columns a thread the larger RN, fewer lanes to add up; with one the smaller, more threads)
+        if (ln * rns[i] < best_cover || (quad && ln * rns[i] == best_cover)) best_cover = ln * rns[i], best_rn = rns[i], best_ln = ln;
     }
-    const int LN = best_ln, CPB = SCAN_THREADS / LN;
-    int TT = 32;
+    const int LN = best_ln, CQ = quad ? 4 : 1, CPB = (SCAN_THREADS / LN) * CQ;
     const int NS = LN * best_rn;
+    int TT = 32;
     while (TT > 1 && (size_t)TT * (2 * NS + CPB + 2) * sizeof(float) > 46 * 1024) TT /= 2;
     const size_t smem = (size_t)TT * (2 * NS + CPB + 2) * sizeof(float);
     dim3 grid((P + CPB - 1) / CPB, Hs, n_seqs);
     const int vec = N % 4 == 0 && ldx % 4 == 0 && (Hs * P) % 4 == 0 && ((uintptr_t)xbc & 15) == 0;
-#define LGML_SCAN(RN) lgml_launch(ssd_scan_kernel<RN>, grid, SCAN_THREADS, smem, stream, xbc, ldx, dt_raw, ldd, dt_bias, a_log, d_skip, state, \
-                                  state_ld, seq_start, slots, y, ldy, Hs, G, P, N, LN, TT, pieces, zero_start, decay_out, vec)
-    switch (best_rn) {
-        case 8: LGML_SCAN(8); break;
-        case 12: LGML_SCAN(12); break;
-        case 16: LGML_SCAN(16); break;
-        case 24: LGML_SCAN(24); break;
-        default: LGML_SCAN(32); break;
+#define LGML_SCAN(RN, CQ) lgml_launch(ssd_scan_kernel<RN, CQ>, grid, SCAN_THREADS, smem, stream, xbc, ldx, dt_raw, ldd, dt_bias, a_log, d_skip, state, \
+                                      state_ld, seq_start, slots, y, ldy, Hs, G, P, N, LN, TT, pieces, zero_start, decay_out, vec)
+    if (quad) {
+        switch (best_rn) {
+            case 4: LGML_SCAN(4, 4); break;
+            case 8: LGML_SCAN(8, 4); break;
+            case 12: LGML_SCAN(12, 4); break;
+            default: LGML_SCAN(16, 4); break;
+        }
+    } else {
+        switch (best_rn) {
+            case 8: LGML_SCAN(8, 1); break;
+            case 12: LGML_SCAN(12, 1); break;
+            case 16: LGML_SCAN(16, 1); break;
+            case 24: LGML_SCAN(24, 1); break;
+            default: LGML_SCAN(32, 1); break;
+        }
     }
 #undef LGML_SCAN
     return lgml_launch_status("ssd_scan");

@@ -61,7 +61,7 @@ ODD = config(61, 36, [
 # Heads of 64 and 128 entries (the tcgen05 prompt attention in bfloat16), a state of 128 numbers, a loop over all
 # layers that runs twice, no convolution on what the sublayers read.
 WIDE_HEADS = config(101, 96, [
-    parallel(left(4, 2, 64, 64, 4, 0.125, base=250000.0, dims=32, scaling=(8.0, 128, 32.0, 1.0), softcap=20.0), right(3, 32, 128, 1, 4, 3), ff=72),
+    parallel(left(4, 2, 64, 64, 4, 0.11, base=150000.0, dims=48, scaling=(6.0, 128, 24.0, 1.0), softcap=25.0), right(3, 32, 128, 1, 4, 3), ff=72),
     parallel(left(2, 1, 128, 128, 2, 0.09, base=10000.0, dims=64, softcap=15.0), right(6, 16, 64, 2, 3, 2), ff=64),
 ], eps=1e-5, scale=4.0, loop=(0, 2, 2))
 

@@ -246,7 +246,7 @@ def attention_case(H, G, D, Dv, taps, dims, scaling, softcap, T, seed, loud):
 
 @pytest.mark.parametrize("dtype,form", [(torch.float32, "general"), (torch.bfloat16, "general"), (torch.bfloat16, "split"), (torch.bfloat16, "tensor")])
 @pytest.mark.parametrize("shape", [(4, 2, 16, 16, 4, 8, (4.0, 64, 8.0, 1.0), 8.0), (3, 3, 24, 20, 2, 24, None, 30.0), (1, 1, 12, 12, 1, 4, None, None),
-                                   (4, 2, 64, 64, 4, 32, (8.0, 128, 32.0, 1.0), 20.0), (2, 1, 128, 128, 3, 64, None, 15.0),
+                                   (4, 2, 64, 64, 4, 48, (6.0, 128, 24.0, 1.0), 25.0), (2, 1, 128, 128, 3, 64, None, 15.0),
                                    (2, 2, 48, 16, 3, 24, None, 10.0), (6, 2, 8, 4, 4, 2, None, 3.0)])
 @pytest.mark.parametrize("T,loud", [(150, 0), (150, 63), (150, 64), (131, 100), (70, 69)])
 def test_convolved_rotated_keys_as_values_under_a_cap_with_a_sink(dtype, form, shape, T, loud):
@@ -337,6 +337,7 @@ ALONE = {
                                                  L.right(1, 4, 4, 1, 2, 1), ff=24)], eps=1e-5, scale=3.0),
     "recurrence_wide": L.config(53, 40, [L.parallel(L.left(1, 1, 8, 8, 2, 0.3, dims=4), L.right(5, 16, 24, 5, 4, 5), ff=24)], eps=1e-5),
     "input_convolution": L.config(53, 40, [L.parallel(L.left(2, 1, 8, 6, 2, 0.3, dims=8), L.right(2, 4, 6, 2, 2, 2), ff=72)], eps=1e-5, taps=5),
+    "one_tap_everywhere": L.config(53, 40, [L.parallel(L.left(2, 1, 8, 8, 1, 0.3, dims=4), L.right(2, 4, 6, 1, 1, 2), ff=24)], eps=1e-5, taps=1),
     "loop_of_one": L.config(53, 40, [L.parallel(L.left(2, 1, 8, 8, 2, 0.3, dims=4), L.right(2, 4, 6, 1, 2, 1), ff=24),
                                      L.parallel(L.left(1, 1, 16, 8, 4, 0.3, dims=16, softcap=4.0), L.right(4, 6, 10, 2, 3, 4))], eps=1e-5, taps=2,
                             loop=(1, 2, 4)),
