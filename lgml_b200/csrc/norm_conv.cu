@@ -185,17 +185,49 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const float *__restrict
                                                          const float *__restrict__ bias, float *__restrict__ state, long long state_ld,
                                                          const int *__restrict__ seq_of_token, const int *__restrict__ seq_start,
                                                          const int *__restrict__ slots, TO *__restrict__ out, int ld_out, int n, int C, int taps_rt,
-                                                         int act, int residual) {
+                                                         int act, int residual, int tpt) {
     pdl_trigger();
     pdl_wait();
     using X = ConvVec<TO, V>;
     const int taps = TAPS > 0 ? TAPS : taps_rt;
     constexpr int MT = TAPS > 0 ? TAPS : MAX_TAPS;
+    constexpr int RUN = 4;          // tokens a thread takes in a row when a step has many (tpt = RUN): an input row is then read once for RUN results
     const int per_row = C / V;
-    const size_t total = (size_t)n * per_row;
+    const size_t total = (size_t)((n + tpt - 1) / tpt) * per_row;
     const int back = taps - 1;
     for (size_t it = (size_t)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += (size_t)gridDim.x * blockDim.x) {
-        const int t = (int)(it / per_row), c = (int)(it - (size_t)t * per_row) * V;
+      const int tg = (int)(it / per_row), c = (int)(it - (size_t)tg * per_row) * V;
+      const int tA = tg * tpt, tB = min(tA + tpt, n);
+      if (TAPS > 0 && tpt == RUN && tB - tA == RUN) {
+          const int sA = seq_of_token[tA];
+          if (sA == seq_of_token[tA + RUN - 1] && tA - seq_start[sA] >= back) {
+              // RUN tokens of one request, none of which reaches into the slot: a window of back + RUN input rows
+              float in[MT - 1 + RUN][V], wj[MT][V], b[V];
+#pragma unroll
+              for (int e = 0; e < V; ++e) b[e] = 0.f;
+              if (bias) X::load_w(bias + c, b);
+#pragma unroll
+              for (int r = 0; r < MT - 1 + RUN; ++r) X::load(u + (size_t)(tA - back + r) * ld_in + c, in[r]);
+#pragma unroll
+              for (int j = 0; j < MT; ++j) X::load_w(w + (size_t)j * C + c, wj[j]);
+#pragma unroll
+              for (int q = 0; q < RUN; ++q) {
+                  float y[V];
+#pragma unroll
+                  for (int e = 0; e < V; ++e) {
+                      float acc = b[e];
+#pragma unroll
+                      for (int j = 0; j < MT; ++j) acc = fmaf(wj[j][e], in[q + j][e], acc);
+                      if (act == 1) acc = silu_(acc);
+                      if (residual) acc += in[q + MT - 1][e];
+                      y[e] = acc;
+                  }
+                  X::store(out + (size_t)(tA + q) * ld_out + c, y);
+              }
+              continue;
+          }
+      }
+      for (int t = tA; t < tB; ++t) {
         const int s = seq_of_token[t];
         const int t0 = seq_start[s];
         const int i = t - t0;
@@ -282,6 +314,7 @@ __global__ void __launch_bounds__(256) short_conv_kernel(const float *__restrict
                 X::store_f(st + (size_t)r * C, v);
             }
         }
+      }
     }
 }
 
@@ -352,9 +385,10 @@ LGML_API int lgml_short_conv(const float *u, int ld_in, const float *w, const fl
     if (n_tokens == 0) return 0;
     const bool vec = C % 4 == 0 && ld_in % 4 == 0 && ld_out % 4 == 0 && state_ld % 4 == 0 &&
                      ((((uintptr_t)u | (uintptr_t)w | (uintptr_t)bias | (uintptr_t)state) & 15) == 0) && (((uintptr_t)out & 15) == 0);
-    const int grid = grid_for((size_t)n_tokens * (vec ? C / 4 : C), 256);
+    const int tpt = n_tokens >= 256 ? 4 : 1;          // many tokens: a thread takes four in a row
+    const int grid = grid_for((size_t)((n_tokens + tpt - 1) / tpt) * (vec ? C / 4 : C), 256);
 #define LGML_SC(TO, V, T) lgml_launch(short_conv_kernel<TO, V, T>, grid, 256, 0, stream, u, ld_in, w, bias, state, state_ld, seq_of_token, seq_start, \
-                                      slots, (TO *)out, ld_out, n_tokens, C, taps, act, residual)
+                                      slots, (TO *)out, ld_out, n_tokens, C, taps, act, residual, tpt)
 #define LGML_SC_T(TO, V) \
     switch (taps) { case 2: LGML_SC(TO, V, 2); break; case 3: LGML_SC(TO, V, 3); break; case 4: LGML_SC(TO, V, 4); break; default: LGML_SC(TO, V, 0); }
     if (out_dtype == LGML_F32) { if (vec) { LGML_SC_T(float, 4) } else { LGML_SC_T(float, 1) } }

@@ -93,18 +93,18 @@ def test_norm_of_what_is_read_and_of_what_is_added(out_dtype, E):
                                                  (5, 8, "none", False), (8, 12, "silu", True)])
 def test_short_convolution_across_steps_requests_and_reused_slots(out_dtype, taps, C, act, residual):
     """Three requests in slots 2, 0, 3 of 4, their tokens cut into steps of 1, 2, 5 ... tokens (fewer than the taps
-    reach back, more, and none for a request in some steps); then the slots are cleared and used again."""
+    reach back, more, hundreds, and none for a request in some steps); then the slots are cleared and used again."""
     from lgml_b200 import ops
 
     rng = np.random.default_rng(taps * 100 + C)
     w, bias = rng.normal(size=(C, taps)), rng.normal(size=C) if act == "silu" else None
-    lens, slots = [23, 9, 40], [2, 0, 3]
+    lens, slots = [23, 9, 340], [2, 0, 3]
     state = torch.full((4, (taps - 1) * C + 3), 7.0, device=DEV)
     for round_ in range(2):
         us = [rng.normal(size=(n, C + 5)) for n in lens]
         state[slots, :(taps - 1) * C] = 0.0
         done = [0, 0, 0]
-        cuts = [[1, 1, 2, 1, 5, 64], [2, 1, 1, 64], [3, 1, 1, 1, 17, 64]]
+        cuts = [[1, 1, 2, 1, 5, 64], [2, 1, 1, 64], [3, 1, 1, 1, 17, 290, 64]]      # (a step of 256 tokens or more: four tokens a thread)
         got = [np.zeros((n, C)) for n in lens]
         step = 0
         while any(d < n for d, n in zip(done, lens)):
