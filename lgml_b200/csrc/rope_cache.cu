@@ -284,22 +284,21 @@ __global__ void __launch_bounds__(ITEMS) conv_rope_store_kernel(
     T *__restrict__ q_out, int ldq, const int *__restrict__ positions, const int *__restrict__ seq_of_token, const int *__restrict__ seq_start,
     const int *__restrict__ slots, const int *__restrict__ block_table, int max_blocks, const float *__restrict__ inv_freq,
     const float *__restrict__ inv_freq_lo, float mag, int n_rot, T *__restrict__ k_pages, T *__restrict__ v_pages, int n_pages, int page_size,
-    int H, int G, int D, int Dv, int write_kv, int *__restrict__ status) {
+    int H, int G, int D, int Dv, int write_kv, int *__restrict__ status, int n_tokens, int tpt) {
     pdl_trigger();
     pdl_wait();
     using X = CrsVec<V>;
     const int taps = TAPS > 0 ? TAPS : taps_rt;
     constexpr int MT = TAPS > 0 ? TAPS : CONV_MAX_TAPS;      // TAPS > 0: the taps at compile time
-    const int t = blockIdx.x;
+    constexpr int RUN = 4;      // tokens an item takes in a row when a step has many (tpt = RUN): a projected row is then read once for RUN results
     const int half_rot = n_rot / 2, iph = (half_rot + (D - n_rot)) / V;
     const int n_heads = write_kv ? H + G : H;
     const int item = blockIdx.y * ITEMS + threadIdx.x;
     if (item >= n_heads * iph) return;
     const int head = item / iph, j = (item - head * iph) * V;
-    const int s = seq_of_token[t];
-    const int t0 = seq_start[s];
-    const int i = t - t0, back = taps - 1;
-    if (i > 0 && i < back) return;
+    const int back = taps - 1;
+    const int tA = blockIdx.x * tpt, tB = min(tA + tpt, n_tokens);
+    int s = seq_of_token[tA];
     const int d0 = j < half_rot ? j : n_rot + (j - half_rot);
     const int d1 = j < half_rot ? j + half_rot : -1;
     const bool two = d1 >= 0;
@@ -348,6 +347,36 @@ __global__ void __launch_bounds__(ITEMS) conv_rope_store_kernel(
         if (two && d1 < Dv) X::store(v_pages + cell * Dv + d1, b);
     };
 
+    if (TAPS > 0 && tpt == RUN && tB - tA == RUN && s == seq_of_token[tA + RUN - 1] && tA - seq_start[s] >= back) {
+        // RUN tokens of one request, none of which reaches into the slot: a window of back + RUN projected rows
+        float in0[MT - 1 + RUN][V], in1[MT - 1 + RUN][V];
+#pragma unroll
+        for (int r = 0; r < MT - 1 + RUN; ++r) {
+            const float *row = proj + (size_t)(tA - back + r) * ldp;
+            X::load(row + c0, in0[r]);
+            if (two) X::load(row + c1, in1[r]);
+        }
+#pragma unroll
+        for (int q = 0; q < RUN; ++q) {
+            float a[V], b[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                a[e] = b[e] = 0.f;
+#pragma unroll
+                for (int k = 0; k < MT; ++k) {
+                    a[e] = fmaf(w0[k][e], in0[q + k][e], a[e]);
+                    if (two) b[e] = fmaf(w1[k][e], in1[q + k][e], b[e]);
+                }
+            }
+            emit(tA + q, a, b);
+        }
+        return;
+    }
+    for (int t = tA; t < tB; ++t) {
+    s = seq_of_token[t];
+    const int t0 = seq_start[s];
+    const int i = t - t0;
+    if (i > 0 && i < back) continue;
     if (i >= back) {
         float a[V], b[V];
 #pragma unroll
@@ -367,7 +396,7 @@ __global__ void __launch_bounds__(ITEMS) conv_rope_store_kernel(
             }
         }
         emit(t, a, b);
-        return;
+        continue;
     }
     const int n_s = seq_start[s + 1] - t0;
     float *st = state + (size_t)slots[s] * state_ld;
@@ -433,6 +462,7 @@ __global__ void __launch_bounds__(ITEMS) conv_rope_store_kernel(
             if (two) X::store(st + (size_t)r * C + c1, v1);
         }
     }
+    }
 }
 }  // namespace
 
@@ -488,10 +518,11 @@ LGML_API int lgml_conv_rope_store(const float *proj, int ldp, const float *wT, f
                      ((((uintptr_t)proj | (uintptr_t)wT | (uintptr_t)state | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) == 0);
     const int iph = (n_rot / 2 + (D - n_rot)) / (vec ? 4 : 1);
     const int items = (write_kv ? H + G : H) * iph;
-    dim3 grid(n_tokens, (items + ITEMS - 1) / ITEMS);
+    const int tpt = n_tokens >= 256 ? 4 : 1;          // many tokens: an item takes four in a row
+    dim3 grid((n_tokens + tpt - 1) / tpt, (items + ITEMS - 1) / ITEMS);
 #define LGML_CRS_T(T, V, TP) lgml_launch(conv_rope_store_kernel<T, V, TP>, grid, ITEMS, 0, stream, proj, ldp, wT, state, state_ld, taps, (T *)q_out, ldq, positions, \
                                    seq_of_token, seq_start, slots, block_table, max_blocks, inv_freq, inv_freq_lo, mag, n_rot, (T *)k_pages, (T *)v_pages, \
-                                   n_pages, page_size, H, G, D, Dv, write_kv, status)
+                                   n_pages, page_size, H, G, D, Dv, write_kv, status, n_tokens, tpt)
 #define LGML_CRS(T, V) \
     do { switch (taps) { case 2: LGML_CRS_T(T, V, 2); break; case 3: LGML_CRS_T(T, V, 3); break; case 4: LGML_CRS_T(T, V, 4); break; default: LGML_CRS_T(T, V, 0); } } while (0)
     if (dtype == LGML_F32) { if (vec) LGML_CRS(float, 4); else LGML_CRS(float, 1); }
