@@ -179,24 +179,29 @@ __global__ void __launch_bounds__(256) ssd_chain_kernel(float *__restrict__ scra
     *st = S;
 }
 
-// out[t, c] = (y[t, c] silu(z[t, c])) / rms over c's part * w[c]; block (token, part)
-template <typename TO>
-__global__ void __launch_bounds__(1024) ssd_gate_norm_kernel(const float *__restrict__ y, int ldy, const float *__restrict__ z, int ldz,
-                                                            const float *__restrict__ w, TO *__restrict__ out, int ldo, int part, float eps) {
+// out[t, c] = (y[t, c] silu(z[t, c])) / rms over c's part * w[c]; block (token, part).  The gated values wait in shared
+// memory between the sum of squares and the division when a part fits there (keep != 0): y and z are then read once.
+template <typename TO, int NT>
+__global__ void __launch_bounds__(NT) ssd_gate_norm_kernel(const float *__restrict__ y, int ldy, const float *__restrict__ z, int ldz,
+                                                             const float *__restrict__ w, TO *__restrict__ out, int ldo, int part, float eps, int keep) {
     pdl_trigger();
     pdl_wait();
+    extern __shared__ float gated[];
     __shared__ float red[32];
     const int t = blockIdx.x, c0 = blockIdx.y * part;
     const float *yr = y + (size_t)t * ldy + c0, *zr = z + (size_t)t * ldz + c0;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < part; i += blockDim.x) {
+#pragma unroll 4
+    for (int i = threadIdx.x; i < part; i += NT) {
         const float v = act_load(yr + i) * silu_(act_load(zr + i));
+        if (keep) gated[i] = v;
         ss = fmaf(v, v, ss);
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)part + eps);
     TO *orow = out + (size_t)t * ldo + c0;
-    for (int i = threadIdx.x; i < part; i += blockDim.x) {
-        const float v = act_load(yr + i) * silu_(act_load(zr + i));
+#pragma unroll 4
+    for (int i = threadIdx.x; i < part; i += NT) {
+        const float v = keep ? gated[i] : act_load(yr + i) * silu_(act_load(zr + i));
         orow[i] = from_f32<TO>(v * inv * __ldg(w + c0 + i));
     }
 }
@@ -264,12 +269,13 @@ LGML_API int lgml_ssd_gate_norm(const float *y, int ldy, const float *z, int ldz
     dim3 grid(n_tokens, groups);
     const int part = inner / groups;
     const int threads = (n_tokens * groups <= 296 && part >= 1024) ? 1024 : 256;      // few rows: more threads share a row's latency
-    if (out_dtype == LGML_F32)
-        lgml_launch(ssd_gate_norm_kernel<float>, grid, threads, 0, stream, y, ldy, z, ldz, w, (float *)out, ldo, part, eps);
-    else if (out_dtype == LGML_BF16)
-        lgml_launch(ssd_gate_norm_kernel<__nv_bfloat16>, grid, threads, 0, stream, y, ldy, z, ldz, w, (__nv_bfloat16 *)out, ldo, part, eps);
-    else
-        LGML_FAIL("ssd_gate_norm: unknown output type %d", out_dtype);
+    const int keep = (size_t)part * sizeof(float) <= 40 * 1024;
+    const size_t smem = keep ? (size_t)part * sizeof(float) : 0;
+#define LGML_GN(TO, NT) lgml_launch(ssd_gate_norm_kernel<TO, NT>, grid, NT, smem, stream, y, ldy, z, ldz, w, (TO *)out, ldo, part, eps, keep)
+    if (out_dtype == LGML_F32) { if (threads == 1024) LGML_GN(float, 1024); else LGML_GN(float, 256); }
+    else if (out_dtype == LGML_BF16) { if (threads == 1024) LGML_GN(__nv_bfloat16, 1024); else LGML_GN(__nv_bfloat16, 256); }
+    else LGML_FAIL("ssd_gate_norm: unknown output type %d", out_dtype);
+#undef LGML_GN
     return lgml_launch_status("ssd_gate_norm");
 }
 
