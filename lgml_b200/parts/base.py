@@ -15,14 +15,17 @@ Interfaces (tensors are torch tensors on the device; ``rt`` is the ``Runtime``):
 
 * every part:   ``tensor_specs(prefix) -> [TensorSpec]``, ``bind(prefix, tensors, rt)``
 * norm:         ``forward(rt, x_f32, out_dtype, delta=None, rows=None) -> h``
-                (with ``delta``: x += delta first, the sum stays in x)
+                (with ``delta``: x += delta first, the sum stays in x; a norm with ``takes_pending`` also
+                takes a ``PendingDelta``: a result that passes a norm of its own before the sum)
 * position:     ``apply(rt, qkv, batch, cache, n_heads, n_kv_heads, head_dim) -> q``: it owns what
                 happens to q and k between the projection and the cache write, writes this
                 step's k and v into ``cache`` and returns q for attention.  A rotation
                 (``RotaryPosition``) only gives ``n_rot``, ``pairing``, ``inv_freq`` (device
                 float32); any other part calls ``store_kv`` when its own work is done
-* mixer:        ``cache_spec() -> PagedKV | FixedState | None``,
-                ``forward(rt, h, batch, cache) -> delta``  (h, delta: [tokens, width])
+* mixer:        ``cache_spec() -> PagedKV | FixedState | None`` (or a tuple of one of each),
+                ``forward(rt, h, batch, cache) -> delta``  (h, delta: [tokens, width]); a mixer that can stand
+                beside another on the same input (``parts/parallel.py``) also gives ``in_rows() -> (matrix, bias)``
+                and ``forward_projected(rt, proj, batch, cache)``, so that both in-projections are one product
 * feed-forward: ``forward(rt, h) -> delta``; optionally ``first_weights() -> [tensor]``
 * token input:  something a layer carries from token to token, or adds of the token itself, around its
                 mixer and feed-forward (``parts/token_mix.py``)
