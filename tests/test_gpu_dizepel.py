@@ -338,6 +338,8 @@ ALONE = {
     "recurrence_wide": L.config(53, 40, [L.parallel(L.left(1, 1, 8, 8, 2, 0.3, dims=4), L.right(5, 16, 24, 5, 4, 5), ff=24)], eps=1e-5),
     "input_convolution": L.config(53, 40, [L.parallel(L.left(2, 1, 8, 6, 2, 0.3, dims=8), L.right(2, 4, 6, 2, 2, 2), ff=72)], eps=1e-5, taps=5),
     "one_tap_everywhere": L.config(53, 40, [L.parallel(L.left(2, 1, 8, 8, 1, 0.3, dims=4), L.right(2, 4, 6, 1, 1, 2), ff=24)], eps=1e-5, taps=1),
+    "odd_width": L.config(51, 35, [L.parallel(L.left(3, 1, 10, 7, 3, 0.3, dims=6, softcap=7.0), L.right(3, 5, 9, 3, 2, 3), ff=33)], eps=1e-5, scale=1.5, taps=2,
+                          loop=(0, 1, 2)),
     "loop_of_one": L.config(53, 40, [L.parallel(L.left(2, 1, 8, 8, 2, 0.3, dims=4), L.right(2, 4, 6, 1, 2, 1), ff=24),
                                      L.parallel(L.left(1, 1, 16, 8, 4, 0.3, dims=16, softcap=4.0), L.right(4, 6, 10, 2, 3, 4))], eps=1e-5, taps=2,
                             loop=(1, 2, 4)),
@@ -356,6 +358,12 @@ def test_one_mechanism_at_a_time(name, tmp_path):
     for trace in (H.trace_whole(seqs), H.trace_portions(seqs), H.trace_tail(seqs, tail=40)):
         runner = make_runner(folder, "float32", n_pages=4)
         L.compare(H.run_trace(runner, trace), cfg, weights, seqs, **TOL["float32"])
+    if name == "odd_width":
+        # bfloat16 at a width no 16-byte access or tensor-memory copy takes: the products fall to the library, the rest to scalar accesses
+        weights = L.random_weights(cfg, seed=21)
+        folder = L.write_folder(tmp_path / (name + "_bf16"), cfg, weights)
+        runner = make_runner(folder, "bfloat16", n_pages=4)
+        L.compare(H.run_trace(runner, H.trace_portions(seqs)), cfg, weights, seqs, **TOL["bfloat16"])
 
 
 @pytest.fixture(scope="module", params=sorted(L.CONFIGS))
